@@ -1,0 +1,114 @@
+// Causal grouped-query attention over the paged cache for any head size up to 256 and any
+// number of heads and groups, in float32 arithmetic on the CUDA cores, for float32 or
+// bfloat16 storage. One warp per (token, query head) walks the keys of the token's own
+// sequence in tiles of 32 with an online softmax. It serves prefill and decode of the true
+// 32-bit path and is the fallback of the bfloat16 path.
+//
+// The formula is the reference's (paths within the reference project):
+// src/infer/mormot.ai.infer.backend.cpu.pas:1296-1353 — head h reads KV head
+// h div (heads div kv_heads); keys max(0, pos+1-window)..pos; s = q·k·scale; p = exp(s - max);
+// y = (sum p v) / (sum p) — and the tiled form of tools/cuda/ops.cu:352-540.
+#include "common.cuh"
+
+MB_DEFINE_LAST_ERROR
+
+#define ATT_WARPS 4
+#define ATT_MAX_D 8  // head sizes up to 32 * 8
+
+template <typename T>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+                      const T* __restrict__ kpool, const T* __restrict__ vpool,
+                      const int* __restrict__ page_table, int max_pages, int ring_pages,
+                      const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                      const int* __restrict__ seq_slot, int nh, int nkv, int hd, int window,
+                      float scale) {
+  extern __shared__ float qs[];  // ATT_WARPS x hd
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int h = blockIdx.y * ATT_WARPS + warp;
+  if (h >= nh) return;
+  const int g = h / (nh / nkv);
+  const int pos = tok_pos[t];
+  const int slot = seq_slot[tok_seq[t]];
+  float* qv = qs + warp * hd;
+  const T* qp = q + (size_t)t * q_stride + (size_t)h * hd;
+  for (int i = lane; i < hd; i += 32) qv[i] = to_f32<T>(qp[i]);
+  __syncwarp();
+
+  int lo = 0;
+  if (window > 0 && pos + 1 > window) lo = pos + 1 - window;
+  float m = -INFINITY, l = 0.f;
+  float acc[ATT_MAX_D];
+#pragma unroll
+  for (int d = 0; d < ATT_MAX_D; ++d) acc[d] = 0.f;
+
+  for (int k0 = lo; k0 <= pos; k0 += 32) {
+    const int kp = k0 + lane;
+    const bool valid = kp <= pos;
+    size_t row = 0;
+    float s = -INFINITY;
+    if (valid) {
+      row = kv_row(page_table, max_pages, ring_pages, slot, kp, nkv, g);
+      const T* kr = kpool + row * hd;
+      float dot = 0.f;
+      for (int i = 0; i < hd; ++i) dot = fmaf(qv[i], to_f32<T>(kr[i]), dot);
+      s = dot * scale;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);  // 0 on the first tile (m = -inf)
+    const float p = valid ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int d = 0; d < ATT_MAX_D; ++d) acc[d] *= corr;
+    m = m_new;
+    const int n = min(32, pos - k0 + 1);
+    for (int j = 0; j < n; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+      const unsigned lo32 = __shfl_sync(0xffffffffu, (unsigned)(row & 0xffffffffu), j);
+      const unsigned hi32 = __shfl_sync(0xffffffffu, (unsigned)(row >> 32), j);
+      const T* vr = vpool + (((size_t)hi32 << 32) | lo32) * hd;
+#pragma unroll
+      for (int d = 0; d < ATT_MAX_D; ++d) {
+        const int i = lane + 32 * d;
+        if (i < hd) acc[d] = fmaf(pj, to_f32<T>(vr[i]), acc[d]);
+      }
+    }
+  }
+  const float inv = 1.0f / l;
+  T* op = out + (size_t)t * out_stride + (size_t)h * hd;
+#pragma unroll
+  for (int d = 0; d < ATT_MAX_D; ++d) {
+    const int i = lane + 32 * d;
+    if (i < hd) op[i] = from_f32<T>(acc[d] * inv);
+  }
+}
+
+// out[t, h, :] for every token t of the step and head h. q: head h of token t at
+// q + t * q_stride + h * hd (the q part of the fused qkv rows); out likewise with out_stride.
+MB_EXPORT int mb_attention_simt(const void* q, int q_stride, void* out, int out_stride,
+                                const void* kpool, const void* vpool, int dtype,
+                                const int* page_table, int max_pages, int ring_pages,
+                                const int* tok_seq, const int* tok_pos, const int* seq_slot,
+                                int T, int nh, int nkv, int hd, int window, float scale,
+                                void* stream) {
+  if (T <= 0) return 0;
+  if (hd <= 0 || hd > 32 * ATT_MAX_D)
+    MB_FAIL("mb_attention_simt: heads of %d values are not supported (at most %d)", hd,
+            32 * ATT_MAX_D);
+  if (nkv <= 0 || nh % nkv) MB_FAIL("mb_attention_simt: %d heads on %d KV heads", nh, nkv);
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(T, (nh + ATT_WARPS - 1) / ATT_WARPS);
+  const size_t smem = (size_t)ATT_WARPS * hd * sizeof(float);
+  if (dtype == MB_F32)
+    attention_simt_kernel<float><<<grid, ATT_WARPS * 32, smem, s>>>(
+        (const float*)q, q_stride, (float*)out, out_stride, (const float*)kpool,
+        (const float*)vpool, page_table, max_pages, ring_pages, tok_seq, tok_pos, seq_slot, nh,
+        nkv, hd, window, scale);
+  else
+    attention_simt_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, smem, s>>>(
+        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
+        (const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, max_pages,
+        ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, hd, window, scale);
+  MB_CHECK_LAUNCH("mb_attention_simt");
+}

@@ -1,0 +1,83 @@
+// Shared by every kernel file of the library: element types, the error word, reductions.
+//
+// All entry points are extern "C", take device pointers and a stream, launch asynchronously
+// and return 0, or a negative code after storing a message that mb_last_error() returns.
+// Nothing here allocates device memory: the caller owns every buffer.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+enum MbDtype { MB_F32 = 0, MB_BF16 = 1 };
+
+// Cache pages hold this many positions (cache/pages.py uses the same number).
+#define MB_PAGE 64
+
+static thread_local char g_mb_error[512];
+
+#define MB_FAIL(...)                                             \
+  do {                                                           \
+    snprintf(g_mb_error, sizeof(g_mb_error), __VA_ARGS__);       \
+    return -1;                                                   \
+  } while (0)
+
+#define MB_CHECK_LAUNCH(name)                                                   \
+  do {                                                                          \
+    cudaError_t e_ = cudaGetLastError();                                        \
+    if (e_ != cudaSuccess) MB_FAIL("%s: %s", name, cudaGetErrorString(e_));     \
+    return 0;                                                                   \
+  } while (0)
+
+#define MB_EXPORT extern "C" __attribute__((visibility("default")))
+
+#define MB_DEFINE_LAST_ERROR \
+  MB_EXPORT const char* mb_last_error() { return g_mb_error; }
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = (lane < (int)((blockDim.x + 31) >> 5)) ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// Where position `pos` of the sequence in `slot` lies in a pool [pages][kv_heads][MB_PAGE][hd]:
+// the index of its row for KV head `g`. ring_pages > 0: the line keeps a ring of that many pages.
+__device__ __forceinline__ size_t kv_row(const int* __restrict__ page_table, int max_pages,
+                                         int ring_pages, int slot, int pos, int kv_heads, int g) {
+  int lp = pos / MB_PAGE;
+  if (ring_pages > 0) lp %= ring_pages;
+  const int page = page_table[(size_t)slot * max_pages + lp];
+  return ((size_t)page * kv_heads + g) * MB_PAGE + (pos % MB_PAGE);
+}

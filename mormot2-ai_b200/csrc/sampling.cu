@@ -1,0 +1,159 @@
+// Choosing the next token on the device, one block per sequence: arg-max (greedy) and a draw
+// from softmax(logits / temperature).
+//
+// Semantics of the reference's sampler (paths within the reference project):
+//   arg-max   src/infer/mormot.ai.infer.sampler.pas:123-159 — the highest value, the lowest
+//             index on ties, a NaN never chosen unless all are NaN, -0 equal to +0;
+//   draw      src/infer/mormot.ai.infer.sampler.pas:280-342 — softmax in float64 with the
+//             maximum subtracted, NaN and infinities weigh 0, one splitmix64 draw per token
+//             (:222-233), the vocabulary walked in id order.
+// The walk is done in parallel here (per-thread ranges, then a scan), so a draw that falls
+// within rounding of a boundary may pick the neighbouring token.
+#include "common.cuh"
+#include <math.h>
+
+MB_DEFINE_LAST_ERROR
+
+#define SAMPLE_THREADS 1024
+
+struct Best {
+  float v;
+  int i;
+};
+
+// a is better than b: b has no candidate yet, or a is greater, or equal with a lower index
+__device__ __forceinline__ bool better(const Best& a, const Best& b) {
+  if (a.i < 0) return false;
+  if (b.i < 0) return true;
+  return a.v > b.v || (a.v == b.v && a.i < b.i);
+}
+
+__device__ Best block_argmax(const float* __restrict__ row, int V, Best* sh) {
+  Best b = {0.f, -1};
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    if (v != v) continue;  // NaN
+    const Best c = {v, i};
+    if (better(c, b)) b = c;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best c;
+    c.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+    c.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+    if (better(c, b)) b = c;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) sh[warp] = b;
+  __syncthreads();
+  if (warp == 0) {
+    b = lane < (int)(blockDim.x >> 5) ? sh[lane] : Best{0.f, -1};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      Best c;
+      c.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+      c.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+      if (better(c, b)) b = c;
+    }
+    if (lane == 0) sh[0] = b;
+  }
+  __syncthreads();
+  b = sh[0];
+  __syncthreads();
+  if (b.i < 0) b.i = 0;  // all NaN
+  return b;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, size_t stride, int V, int* __restrict__ out) {
+  __shared__ Best sh[32];
+  const Best b = block_argmax(logits + blockIdx.x * stride, V, sh);
+  if (threadIdx.x == 0) out[blockIdx.x] = b.i;
+}
+
+// out[r] = arg-max of logits[r, 0..V)
+MB_EXPORT int mb_argmax(const float* logits, long long stride, int rows, int V, int* out,
+                        void* stream) {
+  if (rows <= 0) return 0;
+  if (V <= 0) MB_FAIL("mb_argmax: a vocabulary of %d", V);
+  argmax_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, (size_t)stride, V, out);
+  MB_CHECK_LAUNCH("mb_argmax");
+}
+
+__device__ __forceinline__ double weight_of(float v, float m, double inv_t) {
+  // NaN or an infinity weighs 0 (+Inf as the best is excluded before)
+  if ((__float_as_uint(v) & 0x7f800000u) == 0x7f800000u) return 0.0;
+  return exp(((double)v - (double)m) * inv_t);
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, size_t stride, int V, double inv_t,
+              const int* __restrict__ state_index, unsigned long long* __restrict__ states,
+              int* __restrict__ out) {
+  __shared__ Best sh[32];
+  __shared__ double sums[SAMPLE_THREADS];
+  __shared__ double target_sh;
+  __shared__ int found;
+  const float* row = logits + blockIdx.x * stride;
+  const Best best = block_argmax(row, V, sh);
+  const unsigned bits = __float_as_uint(best.v);
+  if ((bits & 0x7f800000u) == 0x7f800000u) {  // no finite best: nothing to draw from
+    if (threadIdx.x == 0) out[blockIdx.x] = best.i;
+    return;
+  }
+  // a contiguous range of ids per thread, so that the walk stays in id order
+  const int per = (V + blockDim.x - 1) / blockDim.x;
+  const int i0 = min(V, (int)threadIdx.x * per), i1 = min(V, i0 + per);
+  double mine = 0.0;
+  for (int i = i0; i < i1; ++i) mine += weight_of(row[i], best.v, inv_t);
+  sums[threadIdx.x] = mine;
+  if (threadIdx.x == 0) found = -1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    // exclusive prefix over the threads' ranges, in order; sums[] becomes the prefix
+    double total = 0.0;
+    for (int t = 0; t < (int)blockDim.x; ++t) {
+      const double v = sums[t];
+      sums[t] = total;
+      total += v;
+    }
+    // one splitmix64 draw of this sequence's stream
+    unsigned long long* st = states + state_index[blockIdx.x];
+    unsigned long long z = (*st += 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    const double u = (double)(z >> 11) * (1.0 / 9007199254740992.0);
+    target_sh = u * total;
+  }
+  __syncthreads();
+  const double target = target_sh;
+  const double before = sums[threadIdx.x];
+  if (target >= before && target < before + mine) {
+    double cum = before;
+    for (int i = i0; i < i1; ++i) {
+      const double w = weight_of(row[i], best.v, inv_t);
+      cum += w;
+      if (w > 0.0 && target < cum) {
+        found = i;  // the ranges are disjoint: at most one thread gets here
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) out[blockIdx.x] = found >= 0 ? found : best.i;
+}
+
+// out[r] = a draw from softmax(logits[r] / temperature) with the splitmix64 state
+// states[state_index[r]], which advances by one draw.
+MB_EXPORT int mb_sample(const float* logits, long long stride, int rows, int V,
+                        double temperature, const int* state_index, unsigned long long* states,
+                        int* out, void* stream) {
+  if (rows <= 0) return 0;
+  if (V <= 0) MB_FAIL("mb_sample: a vocabulary of %d", V);
+  if (!(temperature >= 1e-30)) MB_FAIL("mb_sample: a temperature of %g is greedy", temperature);
+  sample_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
+      logits, (size_t)stride, V, 1.0 / temperature, state_index, states, out);
+  MB_CHECK_LAUNCH("mb_sample");
+}

@@ -1,0 +1,85 @@
+"""One pass of the model over a batch: which tokens, of which sequences, at which positions.
+
+The tokens of all sequences are packed one after another (no padding); per token the index of
+its sequence and its position, per sequence its slot, its first packed row and how many
+positions it held before. Parts and kernels read only this. All index arrays live in one
+device buffer that is filled by one copy from pinned host memory.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+
+@dataclass
+class StepContext:
+    T: int                      # tokens in this pass
+    B: int                      # sequences in this pass
+    tok_ids: torch.Tensor       # int32 [T]
+    tok_seq: torch.Tensor       # int32 [T] index of the token's sequence in this pass
+    tok_pos: torch.Tensor       # int32 [T] absolute position
+    seq_slot: torch.Tensor      # int32 [B]
+    seq_start: torch.Tensor     # int32 [B + 1] first packed row of each sequence
+    seq_past: torch.Tensor      # int32 [B] positions held before this pass
+    want_rows: torch.Tensor     # int32 [n_want] packed rows whose logits are wanted
+    n_want: int
+    max_new: int                # most new tokens of one sequence
+    max_len: int                # longest sequence after this pass
+    decode: bool                # every sequence brings exactly one token
+    # host copies, for parts that plan launches from them
+    host_new: List[int]
+    host_past: List[int]
+    host_slots: List[int]
+
+
+class StepBuffers:
+    """Pinned host and device index buffers, reused by every pass."""
+
+    def __init__(self, max_tokens: int, max_seqs: int, device: torch.device):
+        self.max_tokens, self.max_seqs = max_tokens, max_seqs
+        self.size = 4 * max_tokens + 3 * max_seqs + 1
+        self.host = torch.zeros(self.size, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(self.size, dtype=torch.int32, device=device)
+        self.copied = torch.cuda.Event()
+        self.in_flight = False
+
+    def fill(self, seqs: Sequence[Tuple[int, int, Sequence[int], Sequence[int]]]) -> StepContext:
+        """``seqs = [(slot, past, tokens, want)]``; ``want`` are places among ``tokens``."""
+        B = len(seqs)
+        T = sum(len(s[2]) for s in seqs)
+        n_want = sum(len(s[3]) for s in seqs)
+        assert 0 < T <= self.max_tokens and B <= self.max_seqs and n_want <= self.max_tokens
+        if self.in_flight:
+            self.copied.synchronize()  # the last copy must have read the host buffer
+        h = self.host
+        o_ids, o_seq, o_pos = 0, T, 2 * T
+        o_slot, o_start, o_past, o_want = 3 * T, 3 * T + B, 3 * T + 2 * B + 1, 3 * T + 3 * B + 1
+        ids: List[int] = []
+        seq: List[int] = []
+        pos: List[int] = []
+        starts = [0]
+        wants: List[int] = []
+        for b, (slot, past, tokens, want) in enumerate(seqs):
+            n = len(tokens)
+            ids.extend(tokens)
+            seq.extend([b] * n)
+            pos.extend(range(past, past + n))
+            wants.extend(starts[-1] + w for w in want)
+            starts.append(starts[-1] + n)
+        flat = (ids + seq + pos + [s[0] for s in seqs] + starts + [s[1] for s in seqs] + wants)
+        total = len(flat)
+        h[:total] = torch.tensor(flat, dtype=torch.int32)
+        self.dev[:total].copy_(h[:total], non_blocking=True)
+        self.copied.record()
+        self.in_flight = True
+        d = self.dev
+        new = [len(s[2]) for s in seqs]
+        return StepContext(
+            T=T, B=B, tok_ids=d[o_ids:o_ids + T], tok_seq=d[o_seq:o_seq + T],
+            tok_pos=d[o_pos:o_pos + T], seq_slot=d[o_slot:o_slot + B],
+            seq_start=d[o_start:o_start + B + 1], seq_past=d[o_past:o_past + B],
+            want_rows=d[o_want:o_want + n_want], n_want=n_want, max_new=max(new),
+            max_len=max(s[1] + len(s[2]) for s in seqs), decode=all(n == 1 for n in new),
+            host_new=new, host_past=[s[1] for s in seqs], host_slots=[s[0] for s in seqs])

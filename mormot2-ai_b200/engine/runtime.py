@@ -1,0 +1,34 @@
+"""What parts need to know about where and how they compute: the device, the activation
+type (bfloat16, or float32 on the true 32-bit path) and which kernels are allowed."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels as K
+from ..errors import KernelError
+
+
+class Runtime:
+    def __init__(self, dtype: torch.dtype, device: str = "cuda:0", fast_kernels: bool = True):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError(f"activations of {dtype} are not supported (bfloat16 or float32)")
+        K.require_gpu()
+        self.dtype = dtype
+        self.device = torch.device(device)
+        # the tensor-core kernels serve the bfloat16 path only; the 32-bit path multiplies and
+        # adds in float32 throughout
+        self.fast_kernels = fast_kernels and dtype == torch.bfloat16
+
+    def libraries(self):
+        """The kernel libraries that a model of this runtime needs."""
+        libs = ["elementwise", "gemm_simt", "attention_simt", "sampling"]
+        if self.fast_kernels:
+            libs += ["gemm_tc", "attention_mma"]
+        return libs
+
+    def attention(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> None:
+        if self.fast_kernels:
+            from ..parts import attention_fast
+            if attention_fast.run(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale):
+                return
+        K.attention_simt(q, q_stride, out, step, line, nh, nkv, hd, window, scale)

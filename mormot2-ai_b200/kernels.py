@@ -1,0 +1,165 @@
+"""The Python face of the native kernels: each function takes CUDA tensors, checks what the
+kernel cannot check itself, and launches on the current stream. Nothing here computes in
+PyTorch, and nothing falls back: without a GPU or the compiled libraries it raises
+``KernelError``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build
+from .errors import KernelError
+
+F32, BF16 = 0, 1
+EPI_STORE, EPI_ADD, EPI_SWIGLU = 0, 1, 2
+PAGE = 64  # positions per cache page (MB_PAGE in csrc/common.cuh)
+
+_c = ctypes
+_vp, _i, _f, _d, _ll = _c.c_void_p, _c.c_int, _c.c_float, _c.c_double, _c.c_longlong
+
+
+def code_of(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"tensors of {dtype} are not supported by the kernels")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("a kernel was given a tensor that is not on the GPU")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def require_gpu() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: this library computes on a B200 only (no CPU path)")
+    major, minor = torch.cuda.get_device_capability()
+    if major != 10:
+        raise KernelError(f"the kernels are built for sm_100a; this device is sm_{major}{minor}")
+
+
+def _call(libname: str, fn: str, argtypes, *args) -> None:
+    lib = build.load_library(libname)
+    f = getattr(lib, fn)
+    if f.argtypes is None:
+        f.argtypes = argtypes
+        f.restype = _i
+    rc = f(*args)
+    if rc != 0:
+        raise KernelError(lib.mb_last_error().decode(errors="replace"))
+
+
+def _contig(t: torch.Tensor, what: str) -> None:
+    if not t.is_contiguous():
+        raise KernelError(f"{what} is not contiguous")
+
+
+# ------------------------------------------------------------------------------ elementwise
+def embed(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor) -> None:
+    """x[t, :] = table[ids[t], :] as float32."""
+    T, H = x.shape
+    _contig(table, "the embedding"), _contig(x, "x")
+    assert ids.dtype == torch.int32 and x.dtype == torch.float32 and table.shape[1] == H
+    _call("elementwise", "mb_embed", [_vp, _i, _vp, _vp, _i, _i, _i, _vp],
+          _ptr(table), code_of(table.dtype), _ptr(ids), _ptr(x), T, H, table.shape[0], _stream())
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Tensor],
+            rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
+            partial: Optional[torch.Tensor] = None) -> None:
+    """out[r] = w * x[rows[r] or r] / rms(x). ``partial`` [parts, T, H] float32 is first added
+    into x (the split results of the matrix product before)."""
+    H = x.shape[-1]
+    R = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
+    assert x.dtype == torch.float32 and w.numel() == H
+    _contig(x, "x")
+    parts, stride = 0, 0
+    if partial is not None:
+        assert partial.dtype == torch.float32 and partial.is_contiguous()
+        parts, stride = partial.shape[0], partial.stride(0)
+    _call("elementwise", "mb_rmsnorm",
+          [_vp, _vp, _i, _ll, _vp, _i, _f, _vp, _i, _vp, _i, _i, _vp],
+          _ptr(x), _ptr(partial), parts, stride, _ptr(w), code_of(w.dtype), float(eps),
+          _ptr(out), code_of(out.dtype) if out is not None else F32, _ptr(rows), R, H, _stream())
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[T, I] = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype
+    _contig(gate_up, "gate_up"), _contig(out, "out")
+    _call("elementwise", "mb_swiglu", [_vp, _vp, _i, _i, _i, _vp],
+          _ptr(gate_up), _ptr(out), code_of(out.dtype), T, I, _stream())
+
+
+def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, nh, nkv, hd,
+                       write_kv: bool) -> None:
+    """Per-head norm of q and k, rotary positions, q in place, k and v into the cache line."""
+    T = qkv.shape[0]
+    _contig(qkv, "qkv")
+    assert qkv.shape[1] == (nh + 2 * nkv) * hd
+    wd = code_of(q_norm.dtype) if q_norm is not None else F32
+    _call("elementwise", "mb_qk_norm_rope_store",
+          [_vp, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp,
+           _i, _i, _i, _i, _i, _vp],
+          _ptr(qkv), code_of(qkv.dtype), _ptr(q_norm), _ptr(k_norm), wd, float(eps),
+          _ptr(inv_freq), rot_dim, _ptr(step.tok_seq), _ptr(step.tok_pos), _ptr(step.seq_slot),
+          _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(line.k), _ptr(line.v),
+          T, nh, nkv, hd, 1 if write_kv else 0, _stream())
+
+
+# ------------------------------------------------------------------------------ products
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_STORE) -> None:
+    """c = a · wᵀ (store), c += a · wᵀ (add, float32 c), or SwiGLU over w = [gate; up]."""
+    M, K = a.shape
+    N = c.shape[1]
+    assert w.shape[1] == K and w.shape[0] == (2 * N if epilogue == EPI_SWIGLU else N)
+    assert c.shape[0] == M and a.stride(1) == 1 and c.stride(1) == 1
+    _contig(w, "the weight")
+    _call("gemm_simt", "mb_gemm_simt",
+          [_vp, _i, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp],
+          _ptr(a), code_of(a.dtype), a.stride(0), _ptr(w), code_of(w.dtype), _ptr(c),
+          code_of(c.dtype), c.stride(0), M, N, K, epilogue, _stream())
+
+
+# ------------------------------------------------------------------------------ attention
+def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv, hd,
+                   window: int, scale: float) -> None:
+    T = out.shape[0]
+    _contig(out, "out")
+    _call("attention_simt", "mb_attention_simt",
+          [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f,
+           _vp],
+          _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
+          code_of(out.dtype), _ptr(line.page_table), line.max_pages, line.ring_pages,
+          _ptr(step.tok_seq), _ptr(step.tok_pos), _ptr(step.seq_slot), T, nh, nkv, hd,
+          window, float(scale), _stream())
+
+
+# ------------------------------------------------------------------------------ sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    rows, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    _call("sampling", "mb_argmax", [_vp, _ll, _i, _i, _vp, _vp],
+          _ptr(logits), logits.stride(0), rows, V, _ptr(out), _stream())
+
+
+def sample(logits: torch.Tensor, temperature: float, state_index: torch.Tensor,
+           states: torch.Tensor, out: torch.Tensor) -> None:
+    rows, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    assert states.dtype == torch.int64 and state_index.dtype == torch.int32
+    _call("sampling", "mb_sample", [_vp, _ll, _i, _i, _d, _vp, _vp, _vp, _vp],
+          _ptr(logits), logits.stride(0), rows, V, float(temperature), _ptr(state_index),
+          _ptr(states), _ptr(out), _stream())

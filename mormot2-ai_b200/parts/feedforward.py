@@ -1,0 +1,41 @@
+"""SwiGLU feed-forward: x += (silu(h·Wgᵀ) · (h·Wuᵀ)) · Wdᵀ, no bias
+(``decoder.pas:2865-2899``, ``backend.cpu.pas:1827-1833`` of the reference). Gate and up are
+one product whose epilogue applies the activation."""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .base import FEED_FORWARDS, Part, TensorNeed
+from .linear import Linear
+
+
+class SwiGluFfn(Part):
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.inter = int(p["intermediate_size"])
+        self.names = {k: prefix + v for k, v in p["names"].items()}
+
+    def tensors(self) -> List[TensorNeed]:
+        n = self.names
+        return [TensorNeed(n["gate"], (self.inter, self.hidden)),
+                TensorNeed(n["up"], (self.inter, self.hidden)),
+                TensorNeed(n["down"], (self.hidden, self.inter))]
+
+    def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
+        n = self.names
+        g, u = weights[n["gate"]], weights[n["up"]]
+        if g.dtype != u.dtype:
+            g, u = g.float(), u.float()
+        self.gate_up = Linear(torch.cat([g, u], dim=0), rt, swiglu=True)
+        self.down = Linear(weights[n["down"]], rt)
+
+    def forward(self, h, x, step) -> None:
+        act = self.gate_up(h)
+        self.down(act, add_into=x)
+
+
+FEED_FORWARDS.register("swiglu", SwiGluFfn)
