@@ -18,12 +18,26 @@ class Runtime:
         # the tensor-core kernels serve the bfloat16 path only; the 32-bit path multiplies and
         # adds in float32 throughout
         self.fast_kernels = fast_kernels and dtype == torch.bfloat16
+        self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        # scratch of the split matrix products (float32) and the word that kernels set when
+        # one of their bounded waits ran out
+        self.workspace = (torch.empty(16 << 20, dtype=torch.float32, device=self.device)
+                          if self.fast_kernels else None)
+        self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def check(self) -> None:
+        """Raises if a kernel recorded that one of its waits ran out (synchronizes)."""
+        code = int(self.error_word.item())
+        if code:
+            self.error_word.zero_()
+            raise KernelError(f"a kernel gave up a wait (code {code}: 1 load, 2 MMA, "
+                              "3 epilogue); its result is not valid")
 
     def libraries(self):
         """The kernel libraries that a model of this runtime needs."""
         libs = ["elementwise", "gemm_simt", "attention_simt", "sampling"]
         if self.fast_kernels:
-            libs += ["gemm_tc", "attention_mma"]
+            libs += ["gemm_tc"]
         return libs
 
     def attention(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> None:

@@ -163,3 +163,29 @@ def sample(logits: torch.Tensor, temperature: float, state_index: torch.Tensor,
     _call("sampling", "mb_sample", [_vp, _ll, _i, _i, _d, _vp, _vp, _vp, _vp],
           _ptr(logits), logits.stride(0), rows, V, float(temperature), _ptr(state_index),
           _ptr(states), _ptr(out), _stream())
+
+
+# ------------------------------------------------------------------------------ tensor cores
+def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    lib = build.load_library("gemm_tc")
+    f = lib.mb_gemm_tc_supported
+    if f.argtypes is None:
+        f.argtypes = [_vp, _i, _vp, _i, _i, _i]
+        f.restype = _i
+    return bool(f(_ptr(a), a.stride(0), _ptr(w), a.shape[0], w.shape[0], w.shape[1]))
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, add: bool,
+            workspace: Optional[torch.Tensor], error: torch.Tensor, sms: int) -> None:
+    """c = a · wᵀ (or c += for a float32 c) with bfloat16 a [M, K] and w [N, K] on the tensor
+    cores. ``workspace``: float32 scratch for split sums; ``error``: int32 device word."""
+    M, K = a.shape
+    N = w.shape[0]
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+    assert a.stride(1) == 1 and c.stride(1) == 1 and c.shape == (M, N)
+    _contig(w, "the weight")
+    _call("gemm_tc", "mb_gemm_tc",
+          [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _ll, _vp, _i, _vp],
+          _ptr(a), a.stride(0), _ptr(w), _ptr(c), code_of(c.dtype), c.stride(0), M, N, K,
+          1 if add else 0, _ptr(workspace), workspace.numel() if workspace is not None else 0,
+          _ptr(error), sms, _stream())

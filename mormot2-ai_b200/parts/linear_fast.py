@@ -1,0 +1,42 @@
+"""The tensor-core path of ``Linear``: bfloat16 operands through ``csrc/gemm_tc.cu``.
+
+Sizes that the kernel does not take (an inner size that is no multiple of 8, operands that
+are not 16-byte aligned) go back to the float32 multiply-add kernel. SwiGLU runs as the
+product over [gate; up] followed by the activation kernel.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import kernels as K
+
+
+class FastLinear:
+    def __init__(self, weight: torch.Tensor, rt, swiglu: bool):
+        self.weight, self.rt, self.swiglu = weight, rt, swiglu
+
+    @classmethod
+    def maybe(cls, weight: torch.Tensor, rt, swiglu: bool) -> Optional["FastLinear"]:
+        if weight.shape[1] % 8 or weight.data_ptr() % 16:
+            return None
+        return cls(weight, rt, swiglu)
+
+    def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor],
+                 add_into: Optional[torch.Tensor]) -> bool:
+        """True if the product was done here."""
+        if a.dtype != torch.bfloat16 or a.stride(0) % 8 or a.data_ptr() % 16:
+            return False
+        rt = self.rt
+        if self.swiglu:
+            gu = torch.empty((a.shape[0], self.weight.shape[0]), dtype=torch.bfloat16,
+                             device=a.device)
+            K.gemm_tc(a, self.weight, gu, False, rt.workspace, rt.error_word, rt.sms)
+            K.swiglu(gu, out)
+            return True
+        if add_into is not None:
+            K.gemm_tc(a, self.weight, add_into, True, rt.workspace, rt.error_word, rt.sms)
+        else:
+            K.gemm_tc(a, self.weight, out, False, rt.workspace, rt.error_word, rt.sms)
+        return True
