@@ -9,9 +9,11 @@ from .config import (ModelSpec, PartSpec, Qwen3Config, Run, LayerSpec, architect
 from .errors import CacheError, ConfigError, InferError, KernelError, WeightsError
 from .weights import SafeTensorsFolder, write_random_model, write_safetensors
 from .engine import DecoderModel, Engine, Entry, Runtime
+from .sampling import Sampling, sampling_from_config
+from .client import LlmClient
 
 __all__ = ["ModelSpec", "PartSpec", "Qwen3Config", "Run", "LayerSpec", "architectures",
            "config_of_folder", "register_architecture", "CacheError", "ConfigError",
            "InferError", "KernelError", "WeightsError", "SafeTensorsFolder",
            "write_random_model", "write_safetensors", "DecoderModel", "Engine", "Entry",
-           "Runtime"]
+           "Runtime", "Sampling", "sampling_from_config", "LlmClient"]

@@ -157,3 +157,177 @@ MB_EXPORT int mb_sample(const float* logits, long long stride, int rows, int V,
       logits, (size_t)stride, V, 1.0 / temperature, state_index, states, out);
   MB_CHECK_LAUNCH("mb_sample");
 }
+
+// ------------------------------------------------------------------ top-k, top-p, min-p
+// The reference's filters (src/infer/mormot.ai.infer.sampler.pas:343-436 of the reference
+// project), in its order: the candidates are the tokens at or above a threshold that is
+// lowered until it holds all that the filters can keep; they are sorted by logit (higher
+// first, lower id on a tie); top-k keeps k and every token tied with the k-th; top-p keeps the
+// shortest prefix reaching top_p of the mass that top-k kept; min-p keeps tokens at least
+// min_p times as probable as the best; then one draw from what is left.
+// `scratch` holds one 64-bit key per candidate: [rows][scratch_stride], scratch_stride a power
+// of two >= V. A key orders as the reference ranks: ~(logit as ordered integer) in the upper
+// half, the id in the lower half, ascending.
+__device__ __forceinline__ unsigned ordered_bits(float v) {
+  unsigned b = __float_as_uint(v);
+  if ((b << 1) == 0) b = 0;  // -0 as +0
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ double block_sum_double(double v, double* sh) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sh[w];  // in warp order
+    sh[32] = t;
+  }
+  __syncthreads();
+  const double r = sh[32];
+  __syncthreads();
+  return r;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, double inv_t,
+                       int top_k, double top_p, double min_p,
+                       const int* __restrict__ state_index, unsigned long long* __restrict__ states,
+                       unsigned long long* __restrict__ scratch, size_t scratch_stride,
+                       int* __restrict__ out) {
+  __shared__ Best sh[32];
+  __shared__ double dsh[33];
+  __shared__ int count_sh;
+  __shared__ int result_sh;
+  const float* row = logits + blockIdx.x * stride;
+  unsigned long long* keys = scratch + blockIdx.x * scratch_stride;
+  const Best best = block_argmax(row, V, sh);
+  if ((__float_as_uint(best.v) & 0x7f800000u) == 0x7f800000u) {
+    if (threadIdx.x == 0) out[blockIdx.x] = best.i;
+    return;
+  }
+  double mine = 0.0;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) mine += weight_of(row[i], best.v, inv_t);
+  const double sum = block_sum_double(mine, dsh);
+  // weights relative to the best one (which weighs 1): p_i = w_i / sum
+  double t = (top_k > 0 || top_p < 1.0) ? 1e-3 : min_p;
+  int n = 0;
+  for (;;) {
+    int cnt = 0;
+    double above = 0.0;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const double w = weight_of(row[i], best.v, inv_t);
+      const bool finite = (__float_as_uint(row[i]) & 0x7f800000u) != 0x7f800000u;
+      if (finite && w >= t) { ++cnt; above += w; }
+    }
+    above = block_sum_double(above, dsh);
+    n = (int)(block_sum_double((double)cnt, dsh) + 0.5);
+    bool enough = true;
+    if (top_k > 0) enough = n >= top_k;
+    else if (top_p < 1.0) enough = above >= top_p * sum;
+    if (enough || t == 0.0) break;
+    t *= 1e-3;
+    if (t < 1e-300) t = 0.0;
+  }
+  // gather the candidates' keys, pad to a power of two with the largest key
+  if (threadIdx.x == 0) count_sh = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const double w = weight_of(row[i], best.v, inv_t);
+    const bool finite = (__float_as_uint(row[i]) & 0x7f800000u) != 0x7f800000u;
+    if (finite && w >= t) {
+      const int at = atomicAdd(&count_sh, 1);
+      keys[at] = ((unsigned long long)(~ordered_bits(row[i])) << 32) | (unsigned)i;
+    }
+  }
+  __syncthreads();
+  n = count_sh;
+  int np = 1;
+  while (np < n) np <<= 1;
+  for (int i = n + threadIdx.x; i < np; i += blockDim.x) keys[i] = ~0ull;
+  __syncthreads();
+  // bitonic sort, ascending
+  for (int k = 2; k <= np; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = threadIdx.x; i < np; i += blockDim.x) {
+        const int l = i ^ j;
+        if (l > i) {
+          const unsigned long long a = keys[i], b = keys[l];
+          const bool up = (i & k) == 0;
+          if ((a > b) == up) { keys[i] = b; keys[l] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  if (threadIdx.x == 0) {
+    auto id_of = [&](int c) { return (int)(keys[c] & 0xffffffffull); };
+    auto w_of = [&](int c) { return weight_of(row[id_of(c)], best.v, inv_t); };
+    if (top_k > 0 && n > top_k) {
+      int keep = top_k;
+      const float kth = row[id_of(top_k - 1)];
+      while (keep < n && row[id_of(keep)] == kth) ++keep;
+      n = keep;
+    }
+    if (top_p < 1.0) {
+      double mass = sum;
+      if (top_k > 0) {
+        mass = 0.0;
+        for (int c = 0; c < n; ++c) mass += w_of(c);
+      }
+      double cum = 0.0;
+      int keep = n;
+      for (int c = 0; c < n; ++c) {
+        cum += w_of(c);
+        if (cum >= top_p * mass) { keep = c + 1; break; }
+      }
+      n = keep;
+    }
+    if (min_p > 0.0) {
+      int keep = 1;
+      const double w0 = w_of(0);
+      while (keep < n && w_of(keep) >= min_p * w0) ++keep;
+      n = keep;
+    }
+    double kept = 0.0;
+    for (int c = 0; c < n; ++c) kept += w_of(c);
+    unsigned long long* st = states + state_index[blockIdx.x];
+    unsigned long long z = (*st += 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    const double u = (double)(z >> 11) * (1.0 / 9007199254740992.0) * kept;
+    int pick = id_of(0);
+    double cum = 0.0;
+    for (int c = 0; c < n; ++c) {
+      cum += w_of(c);
+      if (u < cum) { pick = id_of(c); break; }
+    }
+    result_sh = pick;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) out[blockIdx.x] = result_sh;
+}
+
+// Like mb_sample, with top_k (0: off), top_p (1: off) and min_p (0: off). `scratch`:
+// rows * scratch_stride 64-bit words, scratch_stride a power of two >= V.
+MB_EXPORT int mb_sample_filtered(const float* logits, long long stride, int rows, int V,
+                                 double temperature, int top_k, double top_p, double min_p,
+                                 const int* state_index, unsigned long long* states,
+                                 unsigned long long* scratch, long long scratch_stride, int* out,
+                                 void* stream) {
+  if (rows <= 0) return 0;
+  if (V <= 0) MB_FAIL("mb_sample_filtered: a vocabulary of %d", V);
+  if (!(temperature >= 1e-30)) MB_FAIL("mb_sample_filtered: a temperature of %g is greedy", temperature);
+  if (top_k < 0 || !(top_p > 0.0 && top_p <= 1.0) || !(min_p >= 0.0 && min_p < 1.0))
+    MB_FAIL("mb_sample_filtered: top_k %d, top_p %g, min_p %g", top_k, top_p, min_p);
+  if (scratch_stride < V || (scratch_stride & (scratch_stride - 1)))
+    MB_FAIL("mb_sample_filtered: a scratch row of %lld words for %d tokens", scratch_stride, V);
+  sample_filtered_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
+      logits, (size_t)stride, V, 1.0 / temperature, top_k, top_p, min_p, state_index, states,
+      scratch, (size_t)scratch_stride, out);
+  MB_CHECK_LAUNCH("mb_sample_filtered");
+}

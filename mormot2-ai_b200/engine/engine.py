@@ -72,6 +72,8 @@ class Engine:
         self.buffers = StepBuffers(self.max_step_tokens, self.max_slots, rt.device)
         self.on_state: Optional[Callable[[str, torch.Tensor], None]] = None
         self.passes = 0  # passes of the model so far (a step of long prompts takes several)
+        self.last_slots: Optional[torch.Tensor] = None   # slots of the last step, on the device
+        self.last_h2d_bytes = 0                          # index bytes copied for the last step
 
     # ------------------------------------------------------------------ making one
     @classmethod
@@ -148,8 +150,12 @@ class Engine:
         out = None
         if n_want and len(passes) > 1:
             out = torch.empty((n_want, self.vocab_size), dtype=torch.float32, device=self.rt.device)
+        self.last_h2d_bytes = 0
+        self.last_passes = len(passes)
         for seqs, dest in passes:
             ctx = self.buffers.fill(seqs)
+            self.last_h2d_bytes += 4 * (3 * ctx.T + 3 * ctx.B + 1 + ctx.n_want)
+            self.last_slots = ctx.seq_slot
             logits = self.model.forward(ctx, self.cache, self.on_state)
             self.passes += 1
             if logits is not None:

@@ -33,6 +33,10 @@ class Runtime:
             raise KernelError(f"a kernel gave up a wait (code {code}: 1 load, 2 MMA, "
                               "3 epilogue); its result is not valid")
 
+    def check_cheap(self) -> None:
+        """Like ``check`` for a caller that has just synchronized anyway."""
+        self.check()
+
     def libraries(self):
         """The kernel libraries that a model of this runtime needs."""
         libs = ["elementwise", "gemm_simt", "attention_simt", "sampling"]

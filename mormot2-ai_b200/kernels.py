@@ -189,3 +189,15 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, add: bool,
           _ptr(a), a.stride(0), _ptr(w), _ptr(c), code_of(c.dtype), c.stride(0), M, N, K,
           1 if add else 0, _ptr(workspace), workspace.numel() if workspace is not None else 0,
           _ptr(error), sms, _stream())
+
+
+def sample_filtered(logits: torch.Tensor, sampling, state_index: torch.Tensor,
+                    states: torch.Tensor, scratch: torch.Tensor, out: torch.Tensor) -> None:
+    rows, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    assert scratch.dtype == torch.int64 and scratch.is_contiguous() and scratch.shape[0] >= rows
+    _call("sampling", "mb_sample_filtered",
+          [_vp, _ll, _i, _i, _d, _i, _d, _d, _vp, _vp, _vp, _ll, _vp, _vp],
+          _ptr(logits), logits.stride(0), rows, V, float(sampling.temperature),
+          int(sampling.top_k), float(sampling.top_p), float(sampling.min_p), _ptr(state_index),
+          _ptr(states), _ptr(scratch), scratch.shape[1], _ptr(out), _stream())

@@ -1,0 +1,204 @@
+"""The engine against the plain implementation on a B200, in float32 and in bfloat16, for both
+tiny configurations: each request alone and whole; the last 32 tokens one by one; batches of
+unequal lengths whose shorter requests end earlier, one batch after another so that slots and
+pages are used again; long decoding; the first tokens of a sequence; prompts cut into passes
+(which also turns the window's ring of pages on)."""
+import numpy as np
+import pytest
+import torch
+
+from mormot2_ai_b200 import CacheError, Engine, Entry, InferError
+from tests.conftest import close
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+
+
+def engine_of(tiny, dtype, **kw):
+    kw.setdefault("max_tokens", 2048)
+    return Engine.from_folder(tiny.folder, dtype=dtype, **kw)
+
+
+def check(got, want, dtype, what):
+    ok, err = close(got, want, dtype)
+    assert ok, f"{what}: relative error {err:.3g} ({dtype})"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_each_request_alone_and_whole(tiny, dtype):
+    eng = engine_of(tiny, dtype)
+    limit = tiny.config.max_position_embeddings
+    for n in tiny.prompt_lens + [limit]:
+        ids = tiny.tokens(n, seed=n)
+        slot = eng.open()
+        out = eng.step([Entry(slot, ids, list(range(n)))])
+        eng.close(slot)
+        check(out.cpu().numpy(), tiny.reference(ids), dtype, f"whole prompt of {n}")
+    eng.rt.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_last_32_tokens_one_by_one(tiny, dtype):
+    eng = engine_of(tiny, dtype)
+    for n in (40, tiny.config.max_position_embeddings - 3):
+        ids = tiny.tokens(n, seed=100 + n)
+        ref = tiny.reference(ids)
+        slot = eng.open()
+        head = n - 32
+        out = eng.step([Entry(slot, ids[:head], [head - 1])])
+        check(out.cpu().numpy(), ref[head - 1:head], dtype, f"prompt end at {head - 1}")
+        for t in range(head, n):
+            out = eng.step([Entry(slot, [ids[t]])])
+            check(out.cpu().numpy(), ref[t:t + 1], dtype, f"decoded token at {t} of {n}")
+        assert eng.length(slot) == n
+        eng.close(slot)
+    eng.rt.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_unequal_batches_with_slot_reuse(tiny, dtype):
+    """Three slots and few pages for seven requests: batches of unequal lengths, the prompts in
+    one step, then one token each; a request that ends leaves the batch and its slot and pages
+    serve the next batch."""
+    eng = engine_of(tiny, dtype, max_tokens=448, max_slots=3)
+    limit = tiny.config.max_position_embeddings
+    lens = tiny.prompt_lens + [2, 65, 33, limit - tiny.decode_steps - 1]
+    decode = [tiny.decode_steps, 3, 1, tiny.decode_steps, 5, 2, tiny.decode_steps][:len(lens)]
+    reqs = [tiny.tokens(n + d, seed=200 + i) for i, (n, d) in enumerate(zip(lens, decode))]
+    refs = [tiny.reference(r) for r in reqs]
+    used_slots = []
+    for b0 in range(0, len(reqs), 3):
+        idx = list(range(b0, min(b0 + 3, len(reqs))))
+        slots = {i: eng.open() for i in idx}
+        used_slots.append(sorted(slots.values()))
+        out = eng.step([Entry(slots[i], reqs[i][:lens[i]]) for i in idx]).cpu().numpy()
+        for row, i in enumerate(idx):
+            check(out[row:row + 1], refs[i][lens[i] - 1:lens[i]], dtype, f"request {i} prompt")
+        at = {i: lens[i] for i in idx}
+        live = list(idx)
+        while live:
+            live = [i for i in live if at[i] < len(reqs[i])]
+            for i in idx:
+                if i not in live and i in slots:
+                    eng.close(slots.pop(i))          # ended earlier: slot and pages go back
+            if not live:
+                break
+            out = eng.step([Entry(slots[i], [reqs[i][at[i]]]) for i in live]).cpu().numpy()
+            for row, i in enumerate(live):
+                check(out[row:row + 1], refs[i][at[i]:at[i] + 1], dtype,
+                      f"request {i} token {at[i]}")
+                at[i] += 1
+    assert used_slots[0] == used_slots[1] == [0, 1, 2]       # the same slots again
+    assert all(eng.book.held_pages(g) == 0 for g in range(len(eng.plans)))
+    assert eng.book.slots.free == 3
+    eng.rt.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_to_the_context_limit(tiny, dtype):
+    eng = engine_of(tiny, dtype)
+    n = tiny.config.max_position_embeddings
+    ids = tiny.tokens(n, seed=300)
+    ref = tiny.reference(ids)
+    slot = eng.open()
+    out = eng.step([Entry(slot, ids[:3])])
+    check(out.cpu().numpy(), ref[2:3], dtype, "prompt")
+    worst = 0.0
+    for t in range(3, n):
+        out = eng.step([Entry(slot, [ids[t]])])
+        ok, err = close(out.cpu().numpy(), ref[t:t + 1], dtype)
+        assert ok, f"token {t}: relative error {err:.3g}"
+        worst = max(worst, err)
+    with pytest.raises(CacheError, match="exceed the context"):
+        eng.step([Entry(slot, [1])])
+    assert eng.length(slot) == n
+    eng.close(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens_of_a_sequence(tiny, dtype):
+    eng = engine_of(tiny, dtype)
+    ids = tiny.tokens(6, seed=400)
+    ref = tiny.reference(ids)
+    slot = eng.open()
+    for t in range(6):                      # from the very first token on, one by one
+        out = eng.step([Entry(slot, [ids[t]])])
+        check(out.cpu().numpy(), ref[t:t + 1], dtype, f"token {t}")
+    eng.close(slot)
+    slot = eng.open()                       # a prompt of one token, then two at once
+    check(eng.step([Entry(slot, ids[:1])]).cpu().numpy(), ref[0:1], dtype, "first token")
+    check(eng.step([Entry(slot, ids[1:3], [0, 1])]).cpu().numpy(), ref[1:3], dtype, "next two")
+    eng.close(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompts_cut_into_passes(tiny, dtype):
+    """A small pass size cuts prompts into several passes of the model (and, for the windowed
+    layer of tiny B, makes its cache a ring of pages smaller than the sequence): same logits."""
+    eng = engine_of(tiny, dtype, prefill_chunk=16, max_step_tokens=40, max_slots=4)
+    if any(p.window for p in eng.plans):
+        assert any(p.ring_pages for p in eng.plans)
+    limit = tiny.config.max_position_embeddings
+    lens = [limit, limit - 60, 37, 16]
+    reqs = [tiny.tokens(n, seed=500 + n) for n in lens]
+    slots = [eng.open() for _ in reqs]
+    wants = [[0, n // 2, n - 1] if n > 2 else [n - 1] for n in lens]
+    before = eng.passes
+    out = eng.step([Entry(s, r, w) for s, r, w in zip(slots, reqs, wants)]).cpu().numpy()
+    assert eng.passes - before >= limit // 16
+    row = 0
+    for r, w in zip(reqs, wants):
+        ref = tiny.reference(r)
+        for place in w:
+            check(out[row:row + 1], ref[place:place + 1], dtype, f"len {len(r)} place {place}")
+            row += 1
+    # decoding goes on from what the passes left (the longer one beyond the ring's first lap)
+    ext = [r + tiny.tokens(4, seed=len(r)) for r in reqs[1:]]
+    for t in range(4):
+        out = eng.step([Entry(s, [e[len(r) + t]]) for s, e, r in
+                        zip(slots[1:], ext, reqs[1:])]).cpu().numpy()
+        for row, (e, r) in enumerate(zip(ext, reqs[1:])):
+            ref = tiny.reference(e[:len(r) + t + 1])
+            check(out[row:row + 1], ref[-1:], dtype, f"decode {t} after passes")
+    eng.rt.check()
+
+
+def test_refused_steps_change_nothing(tiny_a_model):
+    tiny = tiny_a_model
+    eng = engine_of(tiny, "float32", max_tokens=128, max_slots=2)
+    s0, s1 = eng.open(), eng.open()
+    ids = tiny.tokens(10)
+    eng.step([Entry(s0, ids)])
+    held = eng.book.held_pages(0)
+    for bad, match in (([Entry(s0, [tiny.config.vocab_size])], "outside the vocabulary"),
+                       ([Entry(s0, [-1])], "outside the vocabulary"),
+                       ([Entry(s0, [])], "0 tokens"),
+                       ([Entry(s0, [1]), Entry(s0, [2])], "twice"),
+                       ([Entry(s0, [1], [1])], "wanted places"),
+                       ([], "without entries")):
+        with pytest.raises(InferError, match=match):
+            eng.step(bad)
+    with pytest.raises(CacheError, match="not open"):
+        eng.step([Entry(7, [1])])
+    with pytest.raises(CacheError):
+        eng.step([Entry(s0, [1]), Entry(s1, tiny.tokens(128))])     # more pages than there are
+    assert eng.length(s0) == 10 and eng.length(s1) == 0 and eng.book.held_pages(0) == held
+    ref = tiny.reference(ids + [5])
+    out = eng.step([Entry(s0, [5])]).cpu().numpy()
+    check(out, ref[-1:], "float32", "the step after the refusals")
+    with pytest.raises(CacheError):
+        eng.open()                                                   # both slots are held
+
+
+def test_padding_and_batch_mates_change_nothing(tiny_b_model):
+    """The logits of a request do not depend on what else is in the batch."""
+    tiny = tiny_b_model
+    eng = engine_of(tiny, "float32")
+    a, b, c = tiny.tokens(9, 1), tiny.tokens(50, 2), tiny.tokens(3, 3)
+    s = eng.open()
+    alone = eng.step([Entry(s, a, list(range(9)))]).cpu().numpy().copy()
+    eng.close(s)
+    slots = [eng.open() for _ in range(3)]
+    out = eng.step([Entry(slots[0], b), Entry(slots[1], a, list(range(9))),
+                    Entry(slots[2], c)]).cpu().numpy()
+    assert np.abs(out[1:10] - alone).max() <= 2e-6
