@@ -109,6 +109,13 @@ def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, 
     T = qkv.shape[0]
     _contig(qkv, "qkv")
     assert qkv.shape[1] == (nh + 2 * nkv) * hd
+    if rot_dim > 0 and inv_freq is None:
+        raise KernelError("a rotary encoding without its frequencies (is the position "
+                          "encoding bound?)")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() < rot_dim // 2):
+        raise KernelError(f"{inv_freq.numel()} frequencies for {rot_dim} rotating values")
+    if (q_norm is None) != (k_norm is None):
+        raise KernelError("q_norm and k_norm come together")
     wd = code_of(q_norm.dtype) if q_norm is not None else F32
     _call("elementwise", "mb_qk_norm_rope_store",
           [_vp, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp,

@@ -68,8 +68,6 @@ class GqaAttention(Part):
         self.o = Linear(weights[n["o"]], rt)
         self.q_norm = weights.get(n.get("q_norm", ""))
         self.k_norm = weights.get(n.get("k_norm", ""))
-        self.inv_freq, self.rot_dim = (self.position.frequencies() if self.position is not None
-                                       else (None, 0))
 
     def forward(self, h, x, step, line, state, writes_cache: bool) -> None:
         T = h.shape[0]
@@ -85,7 +83,9 @@ class GqaAttention(Part):
             self.split[1](h, out=qkv[:, self.qw:self.qw + self.kvw])
             self.split[2](h, out=qkv[:, self.qw + self.kvw:])
         eps = float(self.head_norm_eps) if self.head_norm_eps is not None else 0.0
-        K.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, eps, self.inv_freq, self.rot_dim,
+        inv_freq, rot_dim = (self.position.frequencies() if self.position is not None
+                             else (None, 0))
+        K.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, eps, inv_freq, rot_dim,
                              step, line, self.nh, nkv, self.hd, writes_cache)
         attn = torch.empty((T, self.qw), dtype=self.rt.dtype, device=h.device)
         self.rt.attention(qkv, width, attn, step, line, self.nh, self.nkv, self.hd,

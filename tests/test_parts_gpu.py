@@ -143,7 +143,7 @@ def test_block_alone(dtype, tiny_b_model):
     model = DecoderModel(tiny.config.to_model_spec())
     layer = model.layers[1]
     weights = {k: torch.tensor(v).to(DT[dtype]).to(DEV) for k, v in tiny.plain_weights.items()}
-    for p in layer.parts() + list(model.positions.values()):
+    for p in list(model.positions.values()) + layer.parts():
         p.bind(weights, rt)
     n = 40
     x0 = torch.randn(n, tiny.config.hidden_size, generator=torch.Generator().manual_seed(3))
