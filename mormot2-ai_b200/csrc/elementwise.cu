@@ -225,3 +225,25 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, int dtype, const void* q_norm, co
 #undef QK_LAUNCH
   MB_CHECK_LAUNCH("mb_qk_norm_rope_store");
 }
+
+// ------------------------------------------------------------------ decode without the host
+// Between two decode steps that run without a host round trip: the tokens just chosen become
+// the next step's input ids and every position moves on by one.
+__global__ void advance_decode_kernel(int* __restrict__ tok_ids, int* __restrict__ tok_pos,
+                                      const int* __restrict__ chosen, int* __restrict__ history,
+                                      int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const int t = chosen[b];
+  tok_ids[b] = t;
+  tok_pos[b] += 1;
+  if (history) history[b] = t;
+}
+
+MB_EXPORT int mb_advance_decode(int* tok_ids, int* tok_pos, const int* chosen, int* history,
+                                int B, void* stream) {
+  if (B <= 0) return 0;
+  advance_decode_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream>>>(tok_ids, tok_pos,
+                                                                          chosen, history, B);
+  MB_CHECK_LAUNCH("mb_advance_decode");
+}

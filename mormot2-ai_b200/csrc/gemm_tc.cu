@@ -21,6 +21,10 @@
 
 MB_DEFINE_LAST_ERROR
 
+static thread_local int g_last_launches = 0;
+// kernels that the last mb_gemm_tc of this thread launched (2 when K was split)
+MB_EXPORT int mb_gemm_tc_last_launches() { return g_last_launches; }
+
 enum { TC_STORE = 0, TC_ADD = 1, TC_PARTIAL = 2 };
 
 #define TC_BM 128
@@ -270,6 +274,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
   }
 #undef GO
   if (rc) return rc;
+  g_last_launches = splits > 1 ? 2 : 1;
   if (splits > 1) {
     const size_t total = (size_t)M * N;
     const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);

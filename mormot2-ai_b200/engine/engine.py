@@ -40,6 +40,13 @@ class Entry:
     want: Optional[Sequence[int]] = None
 
 
+@dataclass
+class _DecodeGraph:
+    graph: "torch.cuda.CUDAGraph"
+    logits: torch.Tensor
+    launches: int
+
+
 class Engine:
     def __init__(self, config, weights: Dict[str, torch.Tensor], rt: Runtime,
                  max_tokens: int = 4096, max_context: Optional[int] = None,
@@ -73,6 +80,9 @@ class Engine:
         self.on_state: Optional[Callable[[str, torch.Tensor], None]] = None
         self.passes = 0  # passes of the model so far (a step of long prompts takes several)
         self.last_slots: Optional[torch.Tensor] = None   # slots of the last step, on the device
+        # decode passes are replayed as CUDA graphs, one per (sequences, wanted rows)
+        self.use_graphs = True
+        self.graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
         self.last_h2d_bytes = 0                          # index bytes copied for the last step
 
     # ------------------------------------------------------------------ making one
@@ -156,7 +166,7 @@ class Engine:
             ctx = self.buffers.fill(seqs)
             self.last_h2d_bytes += 4 * (3 * ctx.T + 3 * ctx.B + 1 + ctx.n_want)
             self.last_slots = ctx.seq_slot
-            logits = self.model.forward(ctx, self.cache, self.on_state)
+            logits = self._forward(ctx)
             self.passes += 1
             if logits is not None:
                 if out is None and len(passes) == 1:
@@ -167,6 +177,66 @@ class Engine:
         for slot, past, tokens, _ in plan:
             self.book.commit(slot, past + len(tokens))
         return out
+
+    # ------------------------------------------------------------------ one pass
+    def _forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        """One pass of the model. A decode pass (one token per sequence) is captured as a CUDA
+        graph the first time its shape occurs and replayed from then on: the index arrays, the
+        page tables and the cache are read from fixed device addresses, so only their contents
+        change between replays. The logits of a replayed pass live in the graph's own buffer
+        and are overwritten by the next replay of the same shape."""
+        if not (self.use_graphs and ctx.decode and self.on_state is None):
+            return self.model.forward(ctx, self.cache, self.on_state)
+        key = (ctx.B, ctx.n_want)
+        g = self.graphs.get(key)
+        if g is None:
+            out = self.model.forward(ctx, self.cache)     # this step's result, computed eagerly
+            self.graphs[key] = self._capture(ctx)         # the same launches, for later steps
+            return out
+        g.graph.replay()
+        K.Launches.count += g.launches
+        return g.logits
+
+    def _capture(self, ctx: StepContext) -> "_DecodeGraph":
+        graph = torch.cuda.CUDAGraph()
+        before = K.Launches.count
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx, self.cache)
+        launches = K.Launches.count - before
+        K.Launches.count = before                         # capturing launched nothing
+        return _DecodeGraph(graph, logits, launches)
+
+    def decode_steps(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int, sampler,
+                     sampling, vocab_limit: Optional[int] = None) -> torch.Tensor:
+        """``n_steps`` decode steps of the sequences in ``slots`` without a host round trip:
+        ``tokens`` are fed first, then each step feeds what the sampler chose in the step before
+        (the token ids and positions move on in device memory). Returns the chosen tokens
+        ``[n_steps, sequences]`` (int32, on the device); the last row is not fed. No stop
+        token is looked at: the caller cuts the rows."""
+        if len(set(slots)) != len(slots) or len(tokens) != len(slots) or n_steps <= 0:
+            raise InferError("decode_steps: one token for each of distinct slots, n_steps > 0")
+        seqs = []
+        for slot, t in zip(slots, tokens):
+            self.book.check_open(slot)
+            if not 0 <= int(t) < self.vocab_size:
+                raise InferError(f"slot {slot}: token {t} is outside the vocabulary")
+            past = self.book.length[slot]
+            if past + n_steps > self.max_context:
+                raise CacheError(f"slot {slot}: {past} + {n_steps} positions exceed the "
+                                 f"context of {self.max_context}")
+            seqs.append((slot, past, [int(t)], [0]))
+        self.cache.map_pages(self.book.reserve([(s, p + n_steps) for s, p, _, _ in seqs]))
+        ctx = self.buffers.fill(seqs)
+        self.last_slots, self.last_passes = ctx.seq_slot, 1
+        history = torch.empty((n_steps, ctx.B), dtype=torch.int32, device=self.rt.device)
+        for i in range(n_steps):
+            logits = self._forward(ctx)
+            chosen = sampler.pick(logits, ctx.seq_slot, sampling, vocab_limit)
+            K.advance_decode(ctx.tok_ids, ctx.tok_pos, chosen, history[i])
+            self.passes += 1
+        for slot, past, _, _ in seqs:
+            self.book.commit(slot, past + n_steps)
+        return history
 
     def _passes(self, plan):
         """Cuts a step into passes of at most ``prefill_chunk`` new tokens per sequence and

@@ -49,7 +49,13 @@ def require_gpu() -> None:
         raise KernelError(f"the kernels are built for sm_100a; this device is sm_{major}{minor}")
 
 
-def _call(libname: str, fn: str, argtypes, *args) -> None:
+class Launches:
+    """How many kernels of this library were launched (a graph replay counts the kernels that
+    were captured into it)."""
+    count = 0
+
+
+def _call(libname: str, fn: str, argtypes, *args, launches: int = 1) -> None:
     lib = build.load_library(libname)
     f = getattr(lib, fn)
     if f.argtypes is None:
@@ -58,6 +64,7 @@ def _call(libname: str, fn: str, argtypes, *args) -> None:
     rc = f(*args)
     if rc != 0:
         raise KernelError(lib.mb_last_error().decode(errors="replace"))
+    Launches.count += launches
 
 
 def _contig(t: torch.Tensor, what: str) -> None:
@@ -196,6 +203,17 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, add: bool,
           _ptr(a), a.stride(0), _ptr(w), _ptr(c), code_of(c.dtype), c.stride(0), M, N, K,
           1 if add else 0, _ptr(workspace), workspace.numel() if workspace is not None else 0,
           _ptr(error), sms, _stream())
+    # the split of K adds one kernel that sums the partial products
+    Launches.count += build.load_library("gemm_tc").mb_gemm_tc_last_launches() - 1
+
+
+def advance_decode(tok_ids: torch.Tensor, tok_pos: torch.Tensor, chosen: torch.Tensor,
+                   history: Optional[torch.Tensor]) -> None:
+    """The chosen tokens become the next step's ids, every position moves on by one."""
+    B = tok_ids.numel()
+    assert chosen.dtype == torch.int32 and chosen.numel() == B
+    _call("elementwise", "mb_advance_decode", [_vp, _vp, _vp, _vp, _i, _vp],
+          _ptr(tok_ids), _ptr(tok_pos), _ptr(chosen), _ptr(history), B, _stream())
 
 
 def sample_filtered(logits: torch.Tensor, sampling, state_index: torch.Tensor,
