@@ -1,0 +1,270 @@
+// Attention over the paged cache on the tensor cores (bfloat16 storage, float32 softmax and
+// accumulation), for head sizes 64 and 128.
+//
+// Decode (`mb_attention_decode`): one new token per sequence. The query heads that share a KV
+// head are the 16 rows of the m16n8k16 MMA, so the keys and values of a sequence are read
+// once for the whole group. The pages of a sequence are split over `splits` CTAs (grid.x), the
+// four warps of a CTA take pages in turn, every warp keeps an online softmax of its own, the
+// warps are merged in shared memory and the splits by a second kernel (the reference's
+// flash-decoding split + `attnmerge`, tools/cuda/ops.cu:325-329, :589-617 of the reference
+// project; its formula src/infer/mormot.ai.infer.backend.cpu.pas:1296-1353). The split count
+// is fixed by the cache's capacity, not by the lengths, so a captured launch stays valid.
+//
+// Operands go from global memory straight into MMA fragments with 16-byte loads: the sum over
+// the head dimension (for q·k) and over the keys (for p·v) does not care about order, so the
+// fragments use a permutation of the dimensions under which every thread's values lie
+// contiguous in memory.
+#include "mma_common.cuh"
+
+MB_DEFINE_LAST_ERROR
+
+typedef __nv_bfloat16 bf16;
+
+#define DEC_WARPS 4
+
+template <int HD>
+__global__ void __launch_bounds__(DEC_WARPS * 32, 2)
+attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kpool,
+                   const bf16* __restrict__ vpool, const int* __restrict__ page_table,
+                   int max_pages, int ring_pages, const int* __restrict__ tok_seq,
+                   const int* __restrict__ tok_pos, const int* __restrict__ seq_slot, int nh,
+                   int nkv, int window, float scale_log2, int pages_per_split,
+                   float* __restrict__ part_o, float* __restrict__ part_ml) {
+  constexpr int CH = HD / 32;  // 32-dim chunks of q·k
+  constexpr int DB = HD / 64;  // 64-dim blocks of p·v
+  __shared__ float sm_m[DEC_WARPS][16], sm_l[DEC_WARPS][16];
+  __shared__ float sm_o[DEC_WARPS][16][HD];
+
+  const int s = blockIdx.x, S = gridDim.x, t = blockIdx.z;
+  const int G = nh / nkv, subs = (G + 15) / 16;
+  const int g = blockIdx.y / subs, sub = blockIdx.y % subs;
+  const int h0 = g * G + sub * 16;
+  const int rows_valid = min(16, G - sub * 16);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = lane >> 2, c = lane & 3;
+
+  const int pos = tok_pos[t];
+  const int slot = seq_slot[tok_seq[t]];
+  const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+  const int p_first = lo / MB_PAGE, p_last = pos / MB_PAGE;
+  const int my_first = p_first + s * pages_per_split;
+  const int my_last = min(p_last, my_first + pages_per_split - 1);
+
+  // q fragments of rows r and r + 8: 8 consecutive dims per 32-dim chunk
+  uint4 qa[CH], qb[CH];
+  {
+    const bf16* q0 = q + (size_t)t * q_stride + (size_t)(h0 + r) * HD + c * 8;
+    const bf16* q1 = q0 + 8 * HD;
+#pragma unroll
+    for (int ch = 0; ch < CH; ++ch) {
+      qa[ch] = r < rows_valid ? ldg16(q0 + ch * 32) : make_uint4(0, 0, 0, 0);
+      qb[ch] = r + 8 < rows_valid ? ldg16(q1 + ch * 32) : make_uint4(0, 0, 0, 0);
+    }
+  }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[DB][8][4];
+#pragma unroll
+  for (int db = 0; db < DB; ++db)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[db][j][e] = 0.f;
+
+  for (int p = my_first + warp; p <= my_last; p += DEC_WARPS) {
+    const int lp = ring_pages > 0 ? p % ring_pages : p;
+    const int page = page_table[(size_t)slot * max_pages + lp];
+    const bf16* kbase = kpool + ((size_t)page * nkv + g) * MB_PAGE * HD;
+    const bf16* vbase = vpool + ((size_t)page * nkv + g) * MB_PAGE * HD;
+    const int key0 = p * MB_PAGE;
+
+    float sc[8][4];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      sc[u][0] = sc[u][1] = sc[u][2] = sc[u][3] = 0.f;
+      const bf16* krow = kbase + (size_t)(u * 8 + r) * HD + c * 8;
+#pragma unroll
+      for (int ch = 0; ch < CH; ++ch) {
+        const uint4 kb = ldg16(krow + ch * 32);
+        mma_bf16(sc[u], qa[ch].x, qb[ch].x, qa[ch].y, qb[ch].y, kb.x, kb.y);
+        mma_bf16(sc[u], qa[ch].z, qb[ch].z, qa[ch].w, qb[ch].w, kb.z, kb.w);
+      }
+    }
+    // mask (the same for every row: one token), scale into the log2 domain, row maxima
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = key0 + u * 8 + 2 * c + e;
+        const bool ok = key >= lo && key <= pos;
+        sc[u][e] = ok ? sc[u][e] * scale_log2 : -INFINITY;
+        sc[u][2 + e] = ok ? sc[u][2 + e] * scale_log2 : -INFINITY;
+        mx0 = fmaxf(mx0, sc[u][e]);
+        mx1 = fmaxf(mx1, sc[u][2 + e]);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    // a page of this split always holds at least one key of [lo, pos], so n0, n1 are finite
+    const float c0 = exp2f(m0 - n0), c1 = exp2f(m1 - n1);
+    m0 = n0;
+    m1 = n1;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        sc[u][e] = exp2f(sc[u][e] - n0);
+        sc[u][2 + e] = exp2f(sc[u][2 + e] - n1);
+        s0 += sc[u][e];
+        s1 += sc[u][2 + e];
+      }
+    }
+    l0 = l0 * c0 + s0;
+    l1 = l1 * c1 + s1;
+#pragma unroll
+    for (int db = 0; db < DB; ++db)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[db][j][0] *= c0;
+        o[db][j][1] *= c0;
+        o[db][j][2] *= c1;
+        o[db][j][3] *= c1;
+      }
+    // p·v: 16 keys a step; logical column q of output tile j is dim db*64 + q*8 + j
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const uint32_t a0 = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+      const uint32_t a1 = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+      const uint32_t a2 = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+      const uint32_t a3 = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+      const bf16* vrow = vbase + (size_t)(kk * 16 + 2 * c) * HD + r * 8;
+#pragma unroll
+      for (int db = 0; db < DB; ++db) {
+        const uint4 va = ldg16(vrow + db * 64);
+        const uint4 vb = ldg16(vrow + HD + db * 64);
+        const uint4 vc = ldg16(vrow + 8 * HD + db * 64);
+        const uint4 vd = ldg16(vrow + 9 * HD + db * 64);
+        const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+        const uint32_t wc[4] = {vc.x, vc.y, vc.z, vc.w}, wd[4] = {vd.x, vd.y, vd.z, vd.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int w = j >> 1;
+          const uint32_t b0 = (j & 1) ? pack_hi(wa[w], wb[w]) : pack_lo(wa[w], wb[w]);
+          const uint32_t b1 = (j & 1) ? pack_hi(wc[w], wd[w]) : pack_lo(wc[w], wd[w]);
+          mma_bf16(o[db][j], a0, a1, a2, a3, b0, b1);
+        }
+      }
+    }
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (c == 0) {
+    sm_m[warp][r] = m0;
+    sm_m[warp][r + 8] = m1;
+    sm_l[warp][r] = l0;
+    sm_l[warp][r + 8] = l1;
+  }
+#pragma unroll
+  for (int db = 0; db < DB; ++db)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int d0 = db * 64 + (2 * c) * 8 + j, d1 = d0 + 8;
+      sm_o[warp][r][d0] = o[db][j][0];
+      sm_o[warp][r][d1] = o[db][j][1];
+      sm_o[warp][r + 8][d0] = o[db][j][2];
+      sm_o[warp][r + 8][d1] = o[db][j][3];
+    }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < rows_valid * HD; idx += blockDim.x) {
+    const int row = idx / HD, d = idx - row * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm_m[w][row]);
+    float L = 0.f, acc = 0.f;
+    if (M > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; ++w) {
+        const float f = exp2f(sm_m[w][row] - M);  // 0 for a warp without pages
+        L += sm_l[w][row] * f;
+        acc += sm_o[w][row][d] * f;
+      }
+    }
+    const size_t at = ((size_t)t * nh + h0 + row) * S + s;
+    part_o[at * HD + d] = acc;
+    if (d == 0) {
+      part_ml[at * 2] = M;
+      part_ml[at * 2 + 1] = L;
+    }
+  }
+}
+
+// out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), the splits in order
+template <int HD>
+__global__ void attn_merge_kernel(const float* __restrict__ part_o,
+                                  const float* __restrict__ part_ml, int S, bf16* __restrict__ out,
+                                  int out_stride, int nh) {
+  const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const size_t at = ((size_t)t * nh + h) * S;
+  float M = -INFINITY;
+  for (int s = 0; s < S; ++s) M = fmaxf(M, part_ml[(at + s) * 2]);
+  float L = 0.f, acc = 0.f;
+  for (int s = 0; s < S; ++s) {
+    const float m = part_ml[(at + s) * 2];
+    if (m == -INFINITY) continue;
+    const float f = exp2f(m - M);
+    L += part_ml[(at + s) * 2 + 1] * f;
+    acc += part_o[(at + s) * HD + d] * f;
+  }
+  out[(size_t)t * out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(acc / L);
+}
+
+// floats of scratch that mb_attention_decode needs for T tokens
+MB_EXPORT long long mb_attention_decode_scratch(int T, int nh, int hd, int splits) {
+  return (long long)T * nh * splits * (hd + 2);
+}
+
+// out[t, h, :] for every token t (each with its own sequence and position: a decode step, or
+// any few tokens). `splits` CTAs share a sequence's pages, `pages_per_split` each; both are
+// chosen by the caller from the cache's capacity (splits * pages_per_split >= the most pages
+// that a sequence can hold in this line). `scratch`: float32, at least
+// mb_attention_decode_scratch(...) values; its contents are not kept between calls.
+MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int out_stride,
+                                  const void* kpool, const void* vpool, const int* page_table,
+                                  int max_pages, int ring_pages, const int* tok_seq,
+                                  const int* tok_pos, const int* seq_slot, int T, int nh, int nkv,
+                                  int hd, int window, float scale, int splits,
+                                  int pages_per_split, float* scratch, long long scratch_floats,
+                                  void* stream) {
+  if (T <= 0) return 0;
+  if (hd != 64 && hd != 128)
+    MB_FAIL("mb_attention_decode: heads of %d values are not supported (64 or 128)", hd);
+  if (nkv <= 0 || nh % nkv) MB_FAIL("mb_attention_decode: %d heads on %d KV heads", nh, nkv);
+  if (splits <= 0 || pages_per_split <= 0) MB_FAIL("mb_attention_decode: %d splits", splits);
+  if (((uintptr_t)q & 15) || (q_stride & 7))
+    MB_FAIL("mb_attention_decode: q is not 16-byte aligned (stride %d)", q_stride);
+  const long long need = mb_attention_decode_scratch(T, nh, hd, splits);
+  if (scratch == nullptr || scratch_floats < need)
+    MB_FAIL("mb_attention_decode: %lld floats of scratch, %lld needed", scratch_floats, need);
+  const int G = nh / nkv, subs = (G + 15) / 16;
+  if (T > 65535) MB_FAIL("mb_attention_decode: %d tokens are too many for one launch", T);
+  cudaStream_t s = (cudaStream_t)stream;
+  float* part_o = scratch;
+  float* part_ml = scratch + (size_t)T * nh * splits * hd;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(splits, nkv * subs, T), mgrid(T, nh);
+#define GO(HD_)                                                                                \
+  attn_decode_kernel<HD_><<<grid, DEC_WARPS * 32, 0, s>>>(                                      \
+      (const bf16*)q, q_stride, (const bf16*)kpool, (const bf16*)vpool, page_table, max_pages, \
+      ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, window, scale_log2, pages_per_split,    \
+      part_o, part_ml);                                                                        \
+  attn_merge_kernel<HD_><<<mgrid, HD_, 0, s>>>(part_o, part_ml, splits, (bf16*)out, out_stride, nh)
+  if (hd == 64) { GO(64); } else { GO(128); }
+#undef GO
+  MB_CHECK_LAUNCH("mb_attention_decode");
+}

@@ -81,7 +81,7 @@ class Engine:
         self.passes = 0  # passes of the model so far (a step of long prompts takes several)
         self.last_slots: Optional[torch.Tensor] = None   # slots of the last step, on the device
         # decode passes are replayed as CUDA graphs, one per (sequences, wanted rows)
-        self.use_graphs = True
+        self.use_graphs = self.model.capturable()
         self.graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
         self.last_h2d_bytes = 0                          # index bytes copied for the last step
 

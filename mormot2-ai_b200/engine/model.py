@@ -52,6 +52,11 @@ class DecoderModel:
             out += l.parts()
         return out
 
+    def capturable(self) -> bool:
+        """Whether a decode pass may be captured as a CUDA graph: every part must allow it."""
+        blocks = [l.block for l in self.layers]
+        return all(getattr(p, "capturable", False) for p in self.parts() + blocks)
+
     def tensors(self) -> List[TensorNeed]:
         seen: Dict[str, TensorNeed] = {}
         for part in self.parts():

@@ -41,7 +41,7 @@ class Runtime:
         """The kernel libraries that a model of this runtime needs."""
         libs = ["elementwise", "gemm_simt", "attention_simt", "sampling"]
         if self.fast_kernels:
-            libs += ["gemm_tc"]
+            libs += ["gemm_tc", "attention_mma"]
         return libs
 
     def attention(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> None:

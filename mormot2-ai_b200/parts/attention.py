@@ -17,6 +17,8 @@ from .linear import Linear
 
 
 class GqaAttention(Part):
+    capturable = True
+
     def __init__(self, spec, prefix: str = "", positions=None):
         super().__init__(spec, prefix)
         p = spec.params

@@ -63,7 +63,13 @@ class StateNeed:
 
 
 class Part:
-    """Base of every part. ``spec.params`` hold its sizes and constants."""
+    """Base of every part. ``spec.params`` hold its sizes and constants.
+
+    ``capturable``: the part's ``forward`` only launches kernels on the current stream, reads
+    nothing back to the host and takes no decision from the contents of a step, so that a decode
+    pass through it can be captured once as a CUDA graph and replayed. A part that does not say
+    so keeps the engine from using graphs."""
+    capturable = False
 
     def __init__(self, spec: PartSpec, prefix: str = ""):
         self.spec = spec

@@ -9,6 +9,8 @@ from .base import BLOCKS, Part
 
 
 class PreNormResidualBlock(Part):
+    capturable = True
+
     def __init__(self, spec, prefix: str = "", mixer=None, feed_forward=None, norms=None):
         super().__init__(spec, prefix)
         self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms

@@ -13,6 +13,8 @@ from .linear import Linear
 
 
 class TokenEmbedding(Part):
+    capturable = True
+
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
         self.name = spec.params["name"]
@@ -29,6 +31,8 @@ class TokenEmbedding(Part):
 
 
 class LmHead(Part):
+    capturable = True
+
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
         p = spec.params

@@ -12,6 +12,8 @@ from .linear import Linear
 
 
 class SwiGluFfn(Part):
+    capturable = True
+
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
         p = spec.params

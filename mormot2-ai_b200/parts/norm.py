@@ -11,6 +11,8 @@ from .base import NORMS, Part, TensorNeed
 
 
 class RmsNorm(Part):
+    capturable = True
+
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
         self.size = int(spec.params["size"])

@@ -28,6 +28,8 @@ def rope_inverse_frequencies(theta: float, rot_dim: int) -> np.ndarray:
 
 
 class RopeHalf(Part):
+    capturable = True
+
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
         self.theta = float(spec.params["theta"])
@@ -45,6 +47,8 @@ class RopeHalf(Part):
 
 
 class NoPosition(Part):
+    capturable = True
+
     def frequencies(self) -> Tuple[Optional[torch.Tensor], int]:
         return None, 0
 

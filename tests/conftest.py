@@ -35,7 +35,18 @@ def tiny_b():
                        rope_theta=1e6, tie_word_embeddings=False, layer_windows=(0, 24, 0))
 
 
-TINY = {"A": (tiny_a, 0, 0.02, [5, 11, 17], 8), "B": (tiny_b, 1, 0.03, [1, 7, 30, 64], 12)}
+def tiny_c():
+    """Heads of 64 values (the smallest size the tensor-core attention kernels take), groups of
+    two, q width 256 != hidden 128, a window of 70 in the first layer, tied head."""
+    from mormot2_ai_b200 import Qwen3Config
+    return Qwen3Config(vocab_size=384, hidden_size=128, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                       intermediate_size=192, max_position_embeddings=320, rms_norm_eps=1e-6,
+                       rope_theta=5e5, tie_word_embeddings=True, layer_windows=(70, 0))
+
+
+TINY = {"A": (tiny_a, 0, 0.02, [5, 11, 17], 8), "B": (tiny_b, 1, 0.03, [1, 7, 30, 64], 12),
+        "C": (tiny_c, 2, 0.04, [3, 66, 129], 6)}
 
 
 class TinyModel:
@@ -57,7 +68,7 @@ class TinyModel:
         return self.plain.forward(self.plain_config, self.plain_weights, ids)
 
 
-@pytest.fixture(scope="session", params=["A", "B"])
+@pytest.fixture(scope="session", params=["A", "B", "C"])
 def tiny(request, tmp_path_factory):
     return TinyModel(request.param, str(tmp_path_factory.mktemp("tiny_" + request.param)))
 

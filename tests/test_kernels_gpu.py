@@ -155,12 +155,34 @@ def attention_reference(q, keys, values, nh, nkv, hd, pos, window, scale):
     return out
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 1, 48), (3, 3, 80), (8, 2, 128),
-                                       (16, 2, 64), (2, 1, 256)])
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_attention_over_the_paged_cache(nh, nkv, hd, dtype):
-    """Prefill rows and decode rows of three sequences of unequal lengths in one launch, over
-    scrambled pages, with and without a window."""
+def run_attention(kind, q, out, step, line, nh, nkv, hd, window, scale, splits=None):
+    """The general kernel ("simt") or the tensor-core kernel for single tokens ("decode", with
+    the sequence's pages shared out over `splits` CTAs)."""
+    if kind == "simt":
+        K.attention_simt(q, nh * hd, out, step, line, nh, nkv, hd, window, scale)
+        return
+    pages = line.max_pages
+    splits = splits or 3
+    pps = -(-pages // splits)
+    scratch = torch.empty(out.shape[0] * nh * splits * (hd + 2) + 5, device=DEV)
+    K.attention_decode(q, nh * hd, out, step, line, nh, nkv, hd, window, scale,
+                       -(-pages // pps), pps, scratch)
+
+
+ATTENTION_CASES = [("simt", 4, 2, 16, "float32"), ("simt", 6, 1, 48, "float32"),
+                   ("simt", 3, 3, 80, "bfloat16"), ("simt", 8, 2, 128, "float32"),
+                   ("simt", 16, 2, 64, "bfloat16"), ("simt", 2, 1, 256, "bfloat16"),
+                   ("simt", 4, 2, 16, "bfloat16"),
+                   ("decode", 8, 2, 128, "bfloat16"), ("decode", 16, 2, 64, "bfloat16"),
+                   ("decode", 3, 3, 64, "bfloat16"), ("decode", 40, 2, 128, "bfloat16"),
+                   ("decode", 7, 1, 128, "bfloat16")]
+
+
+@pytest.mark.parametrize("kind,nh,nkv,hd,dtype", ATTENTION_CASES)
+def test_attention_over_the_paged_cache(kind, nh, nkv, hd, dtype):
+    """Rows of three sequences of unequal lengths in one launch (the last rows of a long
+    sequence, a sequence of one token, a whole prompt), over scrambled pages, with and without a
+    window; for the tensor-core kernel also with the pages shared out in different ways."""
     rng = np.random.default_rng(nh * hd)
     lens = [200, 1, 77]           # positions already in the cache after this step
     new = [5, 1, 77]              # the last `new` of them are this step's rows
@@ -179,22 +201,25 @@ def test_attention_over_the_paged_cache(nh, nkv, hd, dtype):
         q = torch.tensor(rng.standard_normal((T, nh * hd)), dtype=torch.float32).to(dt)
         out = torch.empty(T, nh * hd, dtype=dt, device=DEV)
         scale = 1.0 / math.sqrt(hd)
-        K.attention_simt(q.to(DEV), nh * hd, out, step, line, nh, nkv, hd, window, scale)
-        got = out.float().cpu().numpy().reshape(T, nh, hd)
-        row = 0
-        for (k, v), n, m in zip(kv, lens, new):
-            for pos in range(n - m, n):
-                want = attention_reference(q[row].float().numpy().reshape(nh, hd), k, v, nh, nkv,
-                                           hd, pos, window, scale)
-                assert rel(got[row], want) <= tol, (window, pos)
-                row += 1
+        for splits in ((None,) if kind == "simt" else (1, 3, 4)):
+            out.zero_()
+            run_attention(kind, q.to(DEV), out, step, line, nh, nkv, hd, window, scale, splits)
+            got = out.float().cpu().numpy().reshape(T, nh, hd)
+            row = 0
+            for (k, v), n, m in zip(kv, lens, new):
+                for pos in range(n - m, n):
+                    want = attention_reference(q[row].float().numpy().reshape(nh, hd), k, v, nh,
+                                               nkv, hd, pos, window, scale)
+                    assert rel(got[row], want) <= tol, (window, splits, pos)
+                    row += 1
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_attention_finds_a_far_key_and_respects_the_windows_edge(dtype):
+@pytest.mark.parametrize("kind,hd,dtype", [("simt", 32, "float32"), ("simt", 32, "bfloat16"),
+                                           ("decode", 64, "bfloat16"), ("decode", 128, "bfloat16")])
+def test_attention_finds_a_far_key_and_respects_the_windows_edge(kind, hd, dtype):
     """One key among 700 matches the query: the output must be that key's value. With a window,
     the matching key just inside the edge is found and the one just outside is not."""
-    nh, nkv, hd, n = 2, 1, 32, 700
+    nh, nkv, n = 2, 1, 700
     dt = DT[dtype]
     rng = np.random.default_rng(3)
     q = rng.standard_normal((nh, hd)).astype(np.float32)
@@ -205,12 +230,15 @@ def test_attention_finds_a_far_key_and_respects_the_windows_edge(dtype):
     for window, far, seen in ((0, 3, True), (100, pos - 99, True), (100, pos - 100, False)):
         kk = k.copy()
         kk[far, 0] = 40.0 * (q[0] + q[1])       # both heads score this key far above the rest
-        line = make_line(2, n, nkv, hd, dt, window=window, seed=window + far)
+        # with a window the line keeps a ring of pages: the key just outside the window is
+        # still stored there and must be left out by its position
+        line = make_line(2, n, nkv, hd, dt, window=window, ring_pages=3 if window else 0,
+                         seed=window + far)
         fill_line(line, 1, torch.tensor(kk), torch.tensor(v))
         step = make_step([(1, pos, [0], [])])
         qd = torch.tensor((q * 8.0).reshape(1, nh * hd)).to(dt).to(DEV)
         out = torch.empty(1, nh * hd, dtype=dt, device=DEV)
-        K.attention_simt(qd, nh * hd, out, step, line, nh, nkv, hd, window, 1.0)
+        run_attention(kind, qd, out, step, line, nh, nkv, hd, window, 1.0, 5)
         got = out.float().cpu().numpy().reshape(nh, hd)
         target = torch.tensor(v[far, 0]).to(dt).float().numpy()
         hit = np.abs(got - target).max() < 2e-2
