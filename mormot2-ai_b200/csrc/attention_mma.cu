@@ -22,6 +22,66 @@ typedef __nv_bfloat16 bf16;
 
 #define DEC_WARPS 4
 
+// scores of one page: sc[u][e] = q(row) · k(key) for the keys u*8 + 2c + (e & 1) of the page and
+// the rows r (e < 2) and r + 8 (e >= 2) of the warp's 16 query rows
+template <int HD>
+__device__ __forceinline__ void qk_page(const uint4* qa, const uint4* qb, const bf16* kbase, int r,
+                                        int c, float sc[8][4]) {
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    sc[u][0] = sc[u][1] = sc[u][2] = sc[u][3] = 0.f;
+    const bf16* krow = kbase + (size_t)(u * 8 + r) * HD + c * 8;
+#pragma unroll
+    for (int ch = 0; ch < HD / 32; ++ch) {
+      const uint4 kb = ldg16(krow + ch * 32);
+      mma_bf16(sc[u], qa[ch].x, qb[ch].x, qa[ch].y, qb[ch].y, kb.x, kb.y);
+      mma_bf16(sc[u], qa[ch].z, qb[ch].z, qa[ch].w, qb[ch].w, kb.z, kb.w);
+    }
+  }
+}
+
+// o += p · v for one page: 16 keys a step; logical column q of output tile j is the dim
+// db*64 + q*8 + j, so a thread ends up with 8 consecutive dims per accumulator column
+template <int HD>
+__device__ __forceinline__ void pv_page(const float sc[8][4], const bf16* vbase, int r, int c,
+                                        float o[HD / 64][8][4]) {
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) {
+    const uint32_t a0 = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+    const uint32_t a1 = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+    const uint32_t a2 = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+    const uint32_t a3 = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+    const bf16* vrow = vbase + (size_t)(kk * 16 + 2 * c) * HD + r * 8;
+#pragma unroll
+    for (int db = 0; db < HD / 64; ++db) {
+      const uint4 va = ldg16(vrow + db * 64);
+      const uint4 vb = ldg16(vrow + HD + db * 64);
+      const uint4 vc = ldg16(vrow + 8 * HD + db * 64);
+      const uint4 vd = ldg16(vrow + 9 * HD + db * 64);
+      const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+      const uint32_t wc[4] = {vc.x, vc.y, vc.z, vc.w}, wd[4] = {vd.x, vd.y, vd.z, vd.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int w = j >> 1;
+        const uint32_t b0 = (j & 1) ? pack_hi(wa[w], wb[w]) : pack_lo(wa[w], wb[w]);
+        const uint32_t b1 = (j & 1) ? pack_hi(wc[w], wd[w]) : pack_lo(wc[w], wd[w]);
+        mma_bf16(o[db][j], a0, a1, a2, a3, b0, b1);
+      }
+    }
+  }
+}
+
+// q fragments of the rows r and r + 8 (null: a row that is not there): 8 consecutive dims per
+// 32-dim chunk and thread
+template <int HD>
+__device__ __forceinline__ void load_q(const bf16* q0, const bf16* q1, int c, uint4* qa, uint4* qb) {
+#pragma unroll
+  for (int ch = 0; ch < HD / 32; ++ch) {
+    qa[ch] = q0 ? ldg16(q0 + ch * 32 + c * 8) : make_uint4(0, 0, 0, 0);
+    qb[ch] = q1 ? ldg16(q1 + ch * 32 + c * 8) : make_uint4(0, 0, 0, 0);
+  }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 2)
 attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kpool,
@@ -53,13 +113,9 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   // q fragments of rows r and r + 8: 8 consecutive dims per 32-dim chunk
   uint4 qa[CH], qb[CH];
   {
-    const bf16* q0 = q + (size_t)t * q_stride + (size_t)(h0 + r) * HD + c * 8;
-    const bf16* q1 = q0 + 8 * HD;
-#pragma unroll
-    for (int ch = 0; ch < CH; ++ch) {
-      qa[ch] = r < rows_valid ? ldg16(q0 + ch * 32) : make_uint4(0, 0, 0, 0);
-      qb[ch] = r + 8 < rows_valid ? ldg16(q1 + ch * 32) : make_uint4(0, 0, 0, 0);
-    }
+    const bf16* qrow = q + (size_t)t * q_stride + (size_t)(h0 + r) * HD;
+    load_q<HD>(r < rows_valid ? qrow : nullptr, r + 8 < rows_valid ? qrow + 8 * HD : nullptr, c,
+               qa, qb);
   }
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   float o[DB][8][4];
@@ -78,17 +134,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     const int key0 = p * MB_PAGE;
 
     float sc[8][4];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      sc[u][0] = sc[u][1] = sc[u][2] = sc[u][3] = 0.f;
-      const bf16* krow = kbase + (size_t)(u * 8 + r) * HD + c * 8;
-#pragma unroll
-      for (int ch = 0; ch < CH; ++ch) {
-        const uint4 kb = ldg16(krow + ch * 32);
-        mma_bf16(sc[u], qa[ch].x, qb[ch].x, qa[ch].y, qb[ch].y, kb.x, kb.y);
-        mma_bf16(sc[u], qa[ch].z, qb[ch].z, qa[ch].w, qb[ch].w, kb.z, kb.w);
-      }
-    }
+    qk_page<HD>(qa, qb, kbase, r, c, sc);
     // mask (the same for every row: one token), scale into the log2 domain, row maxima
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -134,31 +180,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
         o[db][j][2] *= c1;
         o[db][j][3] *= c1;
       }
-    // p·v: 16 keys a step; logical column q of output tile j is dim db*64 + q*8 + j
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-      const uint32_t a0 = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
-      const uint32_t a1 = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
-      const uint32_t a2 = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
-      const uint32_t a3 = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
-      const bf16* vrow = vbase + (size_t)(kk * 16 + 2 * c) * HD + r * 8;
-#pragma unroll
-      for (int db = 0; db < DB; ++db) {
-        const uint4 va = ldg16(vrow + db * 64);
-        const uint4 vb = ldg16(vrow + HD + db * 64);
-        const uint4 vc = ldg16(vrow + 8 * HD + db * 64);
-        const uint4 vd = ldg16(vrow + 9 * HD + db * 64);
-        const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
-        const uint32_t wc[4] = {vc.x, vc.y, vc.z, vc.w}, wd[4] = {vd.x, vd.y, vd.z, vd.w};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int w = j >> 1;
-          const uint32_t b0 = (j & 1) ? pack_hi(wa[w], wb[w]) : pack_lo(wa[w], wb[w]);
-          const uint32_t b1 = (j & 1) ? pack_hi(wc[w], wd[w]) : pack_lo(wc[w], wd[w]);
-          mma_bf16(o[db][j], a0, a1, a2, a3, b0, b1);
-        }
-      }
-    }
+    pv_page<HD>(sc, vbase, r, c, o);
   }
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -267,4 +289,165 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
   if (hd == 64) { GO(64); } else { GO(128); }
 #undef GO
   MB_CHECK_LAUNCH("mb_attention_decode");
+}
+
+// ------------------------------------------------------------------ prefill
+// Causal attention of the new tokens of every sequence over the cache (which already holds
+// their own keys and values). A CTA takes 64 consecutive new tokens of one sequence and one
+// query head; each of its four warps owns 16 of them as the rows of the MMA and walks the pages
+// from the first key its rows may see to the last, with an online softmax per row. The four
+// warps read the same pages, so all but the first read hit the L1 cache.
+template <int HD>
+__global__ void __launch_bounds__(128, 2)
+attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
+                    int out_stride, const bf16* __restrict__ kpool,
+                    const bf16* __restrict__ vpool, const int* __restrict__ page_table,
+                    int max_pages, int ring_pages, const int* __restrict__ seq_start,
+                    const int* __restrict__ seq_past, const int* __restrict__ seq_slot, int nh,
+                    int nkv, int window, float scale_log2) {
+  constexpr int CH = HD / 32, DB = HD / 64;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int start = seq_start[b], n_new = seq_start[b + 1] - start;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = lane >> 2, c = lane & 3;
+  const int row0 = blockIdx.x * 64 + warp * 16;
+  if (row0 >= n_new) return;  // whole warps leave; nothing below synchronizes the CTA
+  const int past = seq_past[b], slot = seq_slot[b];
+  const int g = h / (nh / nkv);
+  const int ra = row0 + r, rb = ra + 8;
+  const bool has_a = ra < n_new, has_b = rb < n_new;
+  const int pa = past + ra, pb = past + rb;  // positions of the two rows
+  const int la = (window > 0 && pa + 1 > window) ? pa + 1 - window : 0;
+  const int lb = (window > 0 && pb + 1 > window) ? pb + 1 - window : 0;
+  const int first_pos = past + row0, last_pos = past + min(row0 + 15, n_new - 1);
+  const int lo_w = (window > 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
+
+  uint4 qa[CH], qb[CH];
+  {
+    const bf16* qrow = q + (size_t)(start + ra) * q_stride + (size_t)h * HD;
+    load_q<HD>(has_a ? qrow : nullptr, has_b ? qrow + (size_t)8 * q_stride : nullptr, c, qa, qb);
+  }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[DB][8][4];
+#pragma unroll
+  for (int db = 0; db < DB; ++db)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[db][j][e] = 0.f;
+
+  for (int p = lo_w / MB_PAGE; p <= last_pos / MB_PAGE; ++p) {
+    const int lp = ring_pages > 0 ? p % ring_pages : p;
+    const int page = page_table[(size_t)slot * max_pages + lp];
+    const bf16* kbase = kpool + ((size_t)page * nkv + g) * MB_PAGE * HD;
+    const bf16* vbase = vpool + ((size_t)page * nkv + g) * MB_PAGE * HD;
+    const int key0 = p * MB_PAGE;
+    float sc[8][4];
+    qk_page<HD>(qa, qb, kbase, r, c, sc);
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = key0 + u * 8 + 2 * c + e;
+        sc[u][e] = (key >= la && key <= pa) ? sc[u][e] * scale_log2 : -INFINITY;
+        sc[u][2 + e] = (key >= lb && key <= pb) ? sc[u][2 + e] * scale_log2 : -INFINITY;
+        mx0 = fmaxf(mx0, sc[u][e]);
+        mx1 = fmaxf(mx1, sc[u][2 + e]);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    // a row may have no key in this page (and none so far): keep exp2 away from inf - inf
+    const float base0 = n0 == -INFINITY ? 0.f : n0, base1 = n1 == -INFINITY ? 0.f : n1;
+    const float c0 = exp2f(m0 - base0), c1 = exp2f(m1 - base1);
+    m0 = n0;
+    m1 = n1;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        sc[u][e] = exp2f(sc[u][e] - base0);
+        sc[u][2 + e] = exp2f(sc[u][2 + e] - base1);
+        s0 += sc[u][e];
+        s1 += sc[u][2 + e];
+      }
+    }
+    l0 = l0 * c0 + s0;
+    l1 = l1 * c1 + s1;
+#pragma unroll
+    for (int db = 0; db < DB; ++db)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[db][j][0] *= c0;
+        o[db][j][1] *= c0;
+        o[db][j][2] *= c1;
+        o[db][j][3] *= c1;
+      }
+    pv_page<HD>(sc, vbase, r, c, o);
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float i0 = 1.0f / l0, i1 = 1.0f / l1;
+  // a thread holds the dims db*64 + 16c .. + 15 of its two rows
+#pragma unroll
+  for (int db = 0; db < DB; ++db) {
+    uint32_t w[4][4];  // [row a lo, row a hi, row b lo, row b hi][4 registers of 2 bf16]
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      w[0][j >> 1] = pack_bf16(o[db][j][0] * i0, o[db][j + 1][0] * i0);
+      w[1][j >> 1] = pack_bf16(o[db][j][1] * i0, o[db][j + 1][1] * i0);
+      w[2][j >> 1] = pack_bf16(o[db][j][2] * i1, o[db][j + 1][2] * i1);
+      w[3][j >> 1] = pack_bf16(o[db][j][3] * i1, o[db][j + 1][3] * i1);
+    }
+    if (has_a) {
+      uint4* dst = (uint4*)(out + (size_t)(start + ra) * out_stride + (size_t)h * HD + db * 64 + 16 * c);
+      dst[0] = make_uint4(w[0][0], w[0][1], w[0][2], w[0][3]);
+      dst[1] = make_uint4(w[1][0], w[1][1], w[1][2], w[1][3]);
+    }
+    if (has_b) {
+      uint4* dst = (uint4*)(out + (size_t)(start + rb) * out_stride + (size_t)h * HD + db * 64 + 16 * c);
+      dst[0] = make_uint4(w[2][0], w[2][1], w[2][2], w[2][3]);
+      dst[1] = make_uint4(w[3][0], w[3][1], w[3][2], w[3][3]);
+    }
+  }
+}
+
+// out[t, h, :] for the new tokens of B sequences (packed one after another: sequence b holds
+// the rows seq_start[b] .. seq_start[b + 1]) over the cache. `max_new`: the most new tokens of
+// one sequence.
+MB_EXPORT int mb_attention_prefill(const void* q, int q_stride, void* out, int out_stride,
+                                   const void* kpool, const void* vpool, const int* page_table,
+                                   int max_pages, int ring_pages, const int* seq_start,
+                                   const int* seq_past, const int* seq_slot, int B, int max_new,
+                                   int nh, int nkv, int hd, int window, float scale,
+                                   void* stream) {
+  if (B <= 0 || max_new <= 0) return 0;
+  if (hd != 64 && hd != 128)
+    MB_FAIL("mb_attention_prefill: heads of %d values are not supported (64 or 128)", hd);
+  if (nkv <= 0 || nh % nkv) MB_FAIL("mb_attention_prefill: %d heads on %d KV heads", nh, nkv);
+  if (((uintptr_t)q & 15) || (q_stride & 7) || ((uintptr_t)out & 15) || (out_stride & 7))
+    MB_FAIL("mb_attention_prefill: q or out is not 16-byte aligned (strides %d, %d)", q_stride,
+            out_stride);
+  if (B > 65535 || nh > 65535) MB_FAIL("mb_attention_prefill: %d sequences, %d heads", B, nh);
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid((max_new + 63) / 64, nh, B);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  if (hd == 64)
+    attn_prefill_kernel<64><<<grid, 128, 0, s>>>(
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kpool, (const bf16*)vpool,
+        page_table, max_pages, ring_pages, seq_start, seq_past, seq_slot, nh, nkv, window,
+        scale_log2);
+  else
+    attn_prefill_kernel<128><<<grid, 128, 0, s>>>(
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kpool, (const bf16*)vpool,
+        page_table, max_pages, ring_pages, seq_start, seq_past, seq_slot, nh, nkv, window,
+        scale_log2);
+  MB_CHECK_LAUNCH("mb_attention_prefill");
 }

@@ -38,4 +38,7 @@ def run(rt, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> bool:
         K.attention_decode(q, q_stride, out, step, line, nh, nkv, hd, window, scale, splits, pps,
                            rt.workspace)
         return True
-    return False
+    if out.stride(0) % 8 or out.data_ptr() % 16:
+        return False
+    K.attention_prefill(q, q_stride, out, step, line, nh, nkv, hd, window, scale)
+    return True

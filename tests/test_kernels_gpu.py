@@ -161,6 +161,9 @@ def run_attention(kind, q, out, step, line, nh, nkv, hd, window, scale, splits=N
     if kind == "simt":
         K.attention_simt(q, nh * hd, out, step, line, nh, nkv, hd, window, scale)
         return
+    if kind == "prefill":
+        K.attention_prefill(q, nh * hd, out, step, line, nh, nkv, hd, window, scale)
+        return
     pages = line.max_pages
     splits = splits or 3
     pps = -(-pages // splits)
@@ -175,7 +178,9 @@ ATTENTION_CASES = [("simt", 4, 2, 16, "float32"), ("simt", 6, 1, 48, "float32"),
                    ("simt", 4, 2, 16, "bfloat16"),
                    ("decode", 8, 2, 128, "bfloat16"), ("decode", 16, 2, 64, "bfloat16"),
                    ("decode", 3, 3, 64, "bfloat16"), ("decode", 40, 2, 128, "bfloat16"),
-                   ("decode", 7, 1, 128, "bfloat16")]
+                   ("decode", 7, 1, 128, "bfloat16"),
+                   ("prefill", 8, 2, 128, "bfloat16"), ("prefill", 16, 2, 64, "bfloat16"),
+                   ("prefill", 3, 3, 64, "bfloat16"), ("prefill", 7, 1, 128, "bfloat16")]
 
 
 @pytest.mark.parametrize("kind,nh,nkv,hd,dtype", ATTENTION_CASES)
@@ -201,7 +206,7 @@ def test_attention_over_the_paged_cache(kind, nh, nkv, hd, dtype):
         q = torch.tensor(rng.standard_normal((T, nh * hd)), dtype=torch.float32).to(dt)
         out = torch.empty(T, nh * hd, dtype=dt, device=DEV)
         scale = 1.0 / math.sqrt(hd)
-        for splits in ((None,) if kind == "simt" else (1, 3, 4)):
+        for splits in ((1, 3, 4) if kind == "decode" else (None,)):
             out.zero_()
             run_attention(kind, q.to(DEV), out, step, line, nh, nkv, hd, window, scale, splits)
             got = out.float().cpu().numpy().reshape(T, nh, hd)
@@ -215,7 +220,8 @@ def test_attention_over_the_paged_cache(kind, nh, nkv, hd, dtype):
 
 
 @pytest.mark.parametrize("kind,hd,dtype", [("simt", 32, "float32"), ("simt", 32, "bfloat16"),
-                                           ("decode", 64, "bfloat16"), ("decode", 128, "bfloat16")])
+                                           ("decode", 64, "bfloat16"), ("decode", 128, "bfloat16"),
+                                           ("prefill", 64, "bfloat16"), ("prefill", 128, "bfloat16")])
 def test_attention_finds_a_far_key_and_respects_the_windows_edge(kind, hd, dtype):
     """One key among 700 matches the query: the output must be that key's value. With a window,
     the matching key just inside the edge is found and the one just outside is not."""
@@ -352,3 +358,34 @@ def test_vocab_limit_is_never_crossed():
     for s in (Sampling(), Sampling(temperature=1.0), Sampling(temperature=1.0, top_k=3)):
         for _ in range(10):
             assert all(t < 50 for t in sampler.pick(logits.to(DEV), slots, s, 50).tolist())
+
+
+@pytest.mark.parametrize("window", [0, 150])
+def test_prefill_attention_of_long_unequal_prompts(window):
+    """The tensor-core prefill kernel over whole prompts of unequal lengths that cross several
+    pages (65, 300, 1 and 129 tokens; the second one continues 70 cached positions)."""
+    nh, nkv, hd = 4, 2, 128
+    rng = np.random.default_rng(window)
+    past = [0, 70, 0, 0]
+    new = [65, 300, 1, 129]
+    line = make_line(4, 512, nkv, hd, torch.bfloat16, window=window, seed=4)
+    kv = []
+    for slot, (p, n) in enumerate(zip(past, new)):
+        k = torch.tensor(rng.standard_normal((p + n, nkv, hd)), dtype=torch.float32).bfloat16().float()
+        v = torch.tensor(rng.standard_normal((p + n, nkv, hd)), dtype=torch.float32).bfloat16().float()
+        fill_line(line, slot, k, v)
+        kv.append((k.numpy(), v.numpy()))
+    step = make_step([(slot, p, [0] * n, []) for slot, (p, n) in enumerate(zip(past, new))])
+    T = sum(new)
+    q = torch.tensor(rng.standard_normal((T, nh * hd)), dtype=torch.float32).bfloat16()
+    out = torch.zeros(T, nh * hd, dtype=torch.bfloat16, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    K.attention_prefill(q.to(DEV), nh * hd, out, step, line, nh, nkv, hd, window, scale)
+    got = out.float().cpu().numpy().reshape(T, nh, hd)
+    row = 0
+    for (k, v), p, n in zip(kv, past, new):
+        for i in list(range(0, n, 7)) + [n - 1]:
+            want = attention_reference(q[row + i].float().numpy().reshape(nh, hd), k, v, nh, nkv,
+                                       hd, p + i, window, scale)
+            assert rel(got[row + i], want) <= 1.2e-2, (window, p, i)
+        row += n
