@@ -204,6 +204,8 @@ def main():
     ap.add_argument("--layers", type=int, default=36, help="fewer layers than the 36 of the shape "
                     "(named in config); the layer sizes stay")
     ap.add_argument("--skip-points", action="store_true", help="no batch 1 / 64 / prefill runs")
+    ap.add_argument("--only-prefill", action="store_true",
+                    help="only the 2,048-token prefill (for profiles; prints its own short line)")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -221,12 +223,16 @@ def main():
 
     pk = peaks()
     cfg = model_config(a.layers)
-    max_batch = BATCH if a.skip_points else 64
+    max_batch = BATCH if (a.skip_points or a.only_prefill) else 64
     eng = Engine.from_random(cfg, seed=2, std=0.02, max_tokens=max_batch * CONTEXT,
                              max_context=CONTEXT, max_slots=max_batch, prefill_chunk=2048,
                              max_step_tokens=8192)
     sampler = DeviceSampler(eng.rt.device, eng.max_slots, eng.vocab_size)
     greedy = Sampling()
+    if a.only_prefill:
+        pms = timed_prefill(torch, eng, PREFILL_TOKENS, repeats=1)
+        print(json.dumps({"prefill_ms": round(pms, 3), "layers": a.layers}))
+        return 0
     clocks = Clocks()
     clocks.start()
     ms, mean_ctx, launches = timed_decode(torch, eng, sampler, greedy, BATCH, a.steps, a.warmup, 1)
