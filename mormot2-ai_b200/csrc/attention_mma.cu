@@ -451,3 +451,49 @@ MB_EXPORT int mb_attention_prefill(const void* q, int q_stride, void* out, int o
         scale_log2);
   MB_CHECK_LAUNCH("mb_attention_prefill");
 }
+
+// ------------------------------------------------------------------ without an allocation
+// See no_alloc.h: the same decode attention with its scratch in an array of the library's own.
+#include "no_alloc.h"
+
+// The scratch itself. In host code this name is only a handle for cudaGetSymbolAddress; it is
+// not a device address and must never be given to a kernel as one.
+static __device__ __align__(256) float g_static_scratch[MB_ATTENTION_DECODE_STATIC_FLOATS];
+
+#define MB_MAX_DEVICES 64
+static float* g_static_scratch_ptr[MB_MAX_DEVICES];  // device address per device, null: not looked up
+
+MB_EXPORT int mb_attention_decode_static(const void* q, int q_stride, void* out, int out_stride,
+                                         const void* kpool, const void* vpool,
+                                         const int* page_table, int max_pages, int ring_pages,
+                                         const int* tok_seq, const int* tok_pos,
+                                         const int* seq_slot, int T, int nh, int nkv, int hd,
+                                         int window, float scale, int splits,
+                                         int pages_per_split, void* stream) {
+  if (T <= 0) return 0;
+  if (nh <= 0 || hd <= 0 || splits <= 0)
+    MB_FAIL("mb_attention_decode_static: %d heads of %d, %d splits", nh, hd, splits);
+  const long long need = mb_attention_decode_scratch(T, nh, hd, splits);
+  if (need > MB_ATTENTION_DECODE_STATIC_FLOATS)
+    MB_FAIL("mb_attention_decode_static: %d tokens x %d heads x %d splits x (%d + 2) = %lld "
+            "values of scratch, the built-in array holds %lld; use fewer splits or "
+            "mb_attention_decode with a buffer of your own",
+            T, nh, splits, hd, need, (long long)MB_ATTENTION_DECODE_STATIC_FLOATS);
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) MB_FAIL("mb_attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= MB_MAX_DEVICES)
+    MB_FAIL("mb_attention_decode_static: device %d (at most %d devices)", device, MB_MAX_DEVICES);
+  if (g_static_scratch_ptr[device] == nullptr) {
+    // once per device, with that device current: the array's address on this device
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      MB_FAIL("mb_attention_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_static_scratch_ptr[device] = p;
+  }
+  return mb_attention_decode(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
+                             ring_pages, tok_seq, tok_pos, seq_slot, T, nh, nkv, hd, window,
+                             scale, splits, pages_per_split, g_static_scratch_ptr[device],
+                             MB_ATTENTION_DECODE_STATIC_FLOATS, stream);
+}

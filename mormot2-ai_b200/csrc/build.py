@@ -38,7 +38,7 @@ SOURCES = {
     "attention_mma": "attention_mma.cu",
 }
 HEADERS = ["common.cuh"]
-EXTRA_HEADERS = {"gemm_tc": ["tc_common.cuh"], "attention_mma": ["mma_common.cuh"]}
+EXTRA_HEADERS = {"gemm_tc": ["tc_common.cuh"], "attention_mma": ["mma_common.cuh", "no_alloc.h"]}
 
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}
