@@ -5,13 +5,14 @@
 // (tools/cuda/linear.cu:418-463, :517-606 of the reference project), without its
 // quantized formats.
 //
-// Epilogues: store; add into a float32 residual; SwiGLU over a weight [2N, K] whose rows
-// [0, N) are the gate and [N, 2N) the up projection (out = silu(gate) * up).
+// Epilogues: store; add into a float32 residual; SwiGLU over a weight [2N, K] (out =
+// silu(gate) * up) whose rows are either [0, N) gate and [N, 2N) up, or alternate gate, up,
+// gate, up ... (the layout that the tensor-core kernel's fused epilogue uses).
 #include "common.cuh"
 
 MB_DEFINE_LAST_ERROR
 
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_SWIGLU_PAIRS = 3 };
 
 #define BM 64
 #define BN 64
@@ -21,7 +22,7 @@ template <typename TA, typename TW, typename TC, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, TC* __restrict__ C,
                  int ldc, int M, int N, int K) {
-  constexpr int NW = EPI == EPI_SWIGLU ? 2 : 1;
+  constexpr int NW = (EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_PAIRS) ? 2 : 1;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[NW][BK][BN + 4];
   const int tid = threadIdx.x;
@@ -46,7 +47,10 @@ gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, TC
       const int gn = n0 + r;
 #pragma unroll
       for (int w = 0; w < NW; ++w)
-        Ws[w][c][r] = (gn < N && gk < K) ? to_f32<TW>(W[((size_t)w * N + gn) * K + gk]) : 0.f;
+        Ws[w][c][r] = (gn < N && gk < K)
+                          ? to_f32<TW>(W[(EPI == EPI_SWIGLU_PAIRS ? (size_t)gn * 2 + w
+                                                                   : (size_t)w * N + gn) * K + gk])
+                          : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -99,19 +103,20 @@ static int launch(const void* A, int lda, const void* W, void* C, int ldc, int M
                                                        ldc, M, N, K)
   if (epi == EPI_STORE) GO(EPI_STORE);
   else if (epi == EPI_ADD) GO(EPI_ADD);
-  else GO(EPI_SWIGLU);
+  else if (epi == EPI_SWIGLU) GO(EPI_SWIGLU);
+  else GO(EPI_SWIGLU_PAIRS);
 #undef GO
   MB_CHECK_LAUNCH("mb_gemm_simt");
 }
 
 // C[M, N] (row stride ldc) = A[M, K] (row stride lda) · W[N, K]ᵀ. For EPI_ADD, C must be
-// float32. For EPI_SWIGLU, W is [2N, K].
+// float32. For the SwiGLU epilogues, W is [2N, K].
 MB_EXPORT int mb_gemm_simt(const void* A, int a_dtype, int lda, const void* W, int w_dtype,
                            void* C, int c_dtype, int ldc, int M, int N, int K, int epilogue,
                            void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) MB_FAIL("mb_gemm_simt: K = %d", K);
-  if (epilogue < 0 || epilogue > 2) MB_FAIL("mb_gemm_simt: epilogue %d", epilogue);
+  if (epilogue < 0 || epilogue > 3) MB_FAIL("mb_gemm_simt: epilogue %d", epilogue);
   if (epilogue == EPI_ADD && c_dtype != MB_F32) MB_FAIL("mb_gemm_simt: the residual is float32");
   cudaStream_t s = (cudaStream_t)stream;
   typedef __nv_bfloat16 bf;

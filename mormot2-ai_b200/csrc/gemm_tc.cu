@@ -8,9 +8,14 @@
 //   few tokens (decode):    the WEIGHT rows on the lanes and the tokens on the columns, so that
 //                           a step streams each weight byte once through full-width MMAs,
 //                           whatever the batch; the tile is written back transposed.
-// When there are fewer tiles than SMs the K range is split over more CTAs; the partial sums
-// go to a float32 workspace that the caller provides and are added up in split order by a
-// second kernel (deterministic, no atomics).
+// In the decode form two CTAs share an SM; a weight with few 128-row tiles has its K range
+// split over as many CTAs as fill those places, one with a few more gets tiles of fewer rows so
+// that one round of CTAs covers it evenly. In the prefill form K is split when there are fewer
+// tiles than SMs. Partial sums go to a float32 workspace that the caller provides and are
+// added up in split order by a second kernel (deterministic, no atomics).
+//
+// Epilogues: store (bfloat16 or float32), add into the float32 residual, and SwiGLU for a
+// weight whose rows alternate gate, up, gate, up ...: out[:, i] = silu(y[:, 2i]) * y[:, 2i+1].
 //
 // Warp roles in a CTA of 192 threads: warp 0 loads (one elected lane), warp 1 allocates TMEM
 // and issues the MMAs (one elected lane), warps 2-5 read the accumulator and store.
@@ -25,20 +30,18 @@ static thread_local int g_last_launches = 0;
 // kernels that the last mb_gemm_tc of this thread launched (2 when K was split)
 MB_EXPORT int mb_gemm_tc_last_launches() { return g_last_launches; }
 
-enum { TC_STORE = 0, TC_ADD = 1, TC_PARTIAL = 2 };
+enum { TC_STORE = 0, TC_ADD = 1, TC_PARTIAL = 2, TC_SWIGLU = 3 };
 
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 192
-#define TC_SMEM_BUDGET (200 * 1024)
+#define TC_A_TILE (TC_BM * TC_BK * 2)  // what an MMA reads from a stage's first operand
+#define TC_MAX_STAGES 32
+#define TC_SMEM_MAX (227 * 1024)
 
 template <int BN> struct TcCfg {
-  static constexpr int A_BYTES = TC_BM * TC_BK * 2;
   static constexpr int B_BYTES = BN * TC_BK * 2;
-  static constexpr int RAW = TC_SMEM_BUDGET / (A_BYTES + B_BYTES);
-  static constexpr int STAGES = RAW > 10 ? 10 : RAW;
   static constexpr int COLS = BN < 32 ? 32 : BN;  // TMEM columns: a power of two >= 32
-  static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ void store_out(void* C, int c_dtype, size_t idx, float v, int mode) {
@@ -50,33 +53,42 @@ __device__ __forceinline__ void store_out(void* C, int c_dtype, size_t idx, floa
   }
 }
 
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
 // rowsA x rowsB outputs: element (a, b) is the dot product of row a of the lanes' operand and
 // row b of the columns' operand. SWAP false: C[a * ldc + b]; true: C[b * ldc + a].
+// A CTA owns `tile_rows` (<= 128) rows of the lanes' operand; its stages hold a_stage bytes of
+// it each (tile_rows rows, rounded up to 8) and BN rows of the other operand.
 template <int BN, bool SWAP>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                void* __restrict__ C, int c_dtype, long long ldc, int rowsA, int rowsB, int K,
                int kb_per_split, int mode, float* __restrict__ partial, long long partial_stride,
-               long long partial_ld, int* __restrict__ error) {
+               long long partial_ld, int tile_rows, int stages, int a_stage,
+               int* __restrict__ error) {
   using Cfg = TcCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
   const uint32_t sA = base;
-  const uint32_t sB = base + Cfg::STAGES * Cfg::A_BYTES;
-  const uint32_t bars = sB + Cfg::STAGES * Cfg::B_BYTES;
-  const uint32_t full0 = bars, empty0 = bars + 8 * Cfg::STAGES, accum = bars + 16 * Cfg::STAGES;
+  // an MMA reads a full 128-row tile from a stage's start: the last stage must have that much
+  // shared memory behind it (rows beyond tile_rows feed TMEM lanes that nobody reads)
+  const uint32_t a_region = max(stages * a_stage, (stages - 1) * a_stage + TC_A_TILE);
+  const uint32_t sB = base + a_region;
+  const uint32_t bars = sB + stages * Cfg::B_BYTES;
+  const uint32_t full0 = bars, empty0 = bars + 8 * stages, accum = bars + 16 * stages;
   const uint32_t slot = accum + 8;
   volatile uint32_t* slot_ptr = (volatile uint32_t*)(smem_raw + (slot - raw));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * BN;
+  const int m0 = blockIdx.x * tile_rows, n0 = blockIdx.y * BN;
   const int nkb_total = (K + TC_BK - 1) / TC_BK;
   const int kb0 = blockIdx.z * kb_per_split;
   const int nkb = min(kb_per_split, nkb_total - kb0);
+  const uint32_t stage_bytes = (uint32_t)tile_rows * (TC_BK * 2) + Cfg::B_BYTES;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::STAGES; ++s) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
@@ -93,29 +105,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp == 0) {
     if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
       for (int i = 0; i < nkb; ++i) {
-        const int s = i % Cfg::STAGES;
-        const uint32_t ph = (i / Cfg::STAGES) & 1;
         mbar_wait(empty0 + 8 * s, ph ^ 1, error, 1);
-        mbar_expect_tx(full0 + 8 * s, Cfg::A_BYTES + Cfg::B_BYTES);
-        tma_load_2d(sA + s * Cfg::A_BYTES, &tmA, (kb0 + i) * TC_BK, m0, full0 + 8 * s);
+        mbar_expect_tx(full0 + 8 * s, stage_bytes);
+        tma_load_2d(sA + s * a_stage, &tmA, (kb0 + i) * TC_BK, m0, full0 + 8 * s);
         tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, (kb0 + i) * TC_BK, n0, full0 + 8 * s);
+        if (++s == stages) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
+      int s = 0;
+      uint32_t ph = 0;
       for (int i = 0; i < nkb; ++i) {
-        const int s = i % Cfg::STAGES;
-        const uint32_t ph = (i / Cfg::STAGES) & 1;
         mbar_wait(full0 + 8 * s, ph, error, 2);
         tc_fence_after_sync();
-        const uint64_t da = umma_desc_k128(sA + s * Cfg::A_BYTES);
+        const uint64_t da = umma_desc_k128(sA + s * a_stage);
         const uint64_t db = umma_desc_k128(sB + s * Cfg::B_BYTES);
 #pragma unroll
         for (int k = 0; k < TC_BK / 16; ++k)  // 16 values of K = 32 bytes further in the row
           umma_bf16(tmem, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
         umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
+        if (++s == stages) { s = 0; ph ^= 1; }
       }
       umma_commit(accum);
     }
@@ -123,7 +137,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     mbar_wait(accum, 0, error, 3);
     tc_fence_after_sync();
     const int q = warp & 3;  // the TMEM lanes a warp may read: 32 * (warp % 4) ..
-    const int a = m0 + q * 32 + lane;
+    const int lane_row = q * 32 + lane;
+    const int a = m0 + lane_row;
+    const bool mine = lane_row < tile_rows && a < rowsA;
     const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
     float* part = partial ? partial + blockIdx.z * partial_stride : nullptr;
 #pragma unroll 1
@@ -131,11 +147,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (n0 + c0 >= rowsB) break;  // uniform over the warp
       float v[16];
       tmem_ld16(taddr + c0, v);
-      if (a >= rowsA) continue;
+      if (SWAP && mode == TC_SWIGLU) {
+        // lanes 2i and 2i+1 hold gate and up of output feature (m0 + lane_row) / 2
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);
+          const int b = n0 + c0 + j;
+          if (mine && !(lane & 1) && b < rowsB)
+            ((__nv_bfloat16*)C)[(size_t)b * ldc + (a >> 1)] = __float2bfloat16_rn(silu_mul(v[j], up));
+        }
+        continue;
+      }
+      if (!mine) continue;
       if (!SWAP) {
         const int b0 = n0 + c0;
         const bool whole = b0 + 16 <= rowsB;
-        if (mode == TC_PARTIAL) {
+        if (mode == TC_SWIGLU) {
+          // columns 2i and 2i+1 are gate and up of output feature (b0 + 2i) / 2
+          __nv_bfloat16* p = (__nv_bfloat16*)C + (size_t)a * ldc + (b0 >> 1);
+          if (whole && (ldc & 7) == 0 && ((uintptr_t)C & 15) == 0) {
+            __nv_bfloat162 h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]),
+                                           silu_mul(v[4 * j + 2], v[4 * j + 3]));
+            *(uint4*)p = *(uint4*)&h[0];
+          } else {
+            for (int j = 0; j < 16 && b0 + j + 1 < rowsB; j += 2)
+              p[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+          }
+        } else if (mode == TC_PARTIAL) {
           float* p = part + (size_t)a * partial_ld + b0;
           if (whole && (partial_ld & 3) == 0 && (partial_stride & 3) == 0) {
 #pragma unroll
@@ -167,9 +208,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             store_out(C, c_dtype, (size_t)a * ldc + b0 + j, v[j], mode);
         }
       } else {
+#pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int b = n0 + c0 + j;
-          if (b >= rowsB) break;
+          if (b >= rowsB) continue;
           if (mode == TC_PARTIAL) part[(size_t)b * partial_ld + a] = v[j];
           else store_out(C, c_dtype, (size_t)b * ldc + a, v[j], mode);
         }
@@ -195,24 +237,41 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
   }
 }
 
+struct TcPlan {
+  int tile_rows, stages, a_stage, smem, splits, kb_per_split;
+};
+
 template <int BN, bool SWAP>
 static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int c_dtype,
-                     long long ldc, int rowsA, int rowsB, int K, int splits, int kb_per_split,
-                     int mode, float* partial, long long pstride, long long pld, int* error,
+                     long long ldc, int rowsA, int rowsB, int K, const TcPlan& p, int mode,
+                     float* partial, long long pstride, long long pld, int* error,
                      cudaStream_t s) {
-  using Cfg = TcCfg<BN>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
-    if (e != cudaSuccess) MB_FAIL("mb_gemm_tc: shared memory of %d bytes: %s", Cfg::SMEM,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_MAX);
+    if (e != cudaSuccess) MB_FAIL("mb_gemm_tc: shared memory of %d bytes: %s", TC_SMEM_MAX,
                                   cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((rowsA + TC_BM - 1) / TC_BM, (rowsB + BN - 1) / BN, splits);
-  gemm_tc_kernel<BN, SWAP><<<grid, TC_THREADS, Cfg::SMEM, s>>>(
-      tmA, tmB, C, c_dtype, ldc, rowsA, rowsB, K, kb_per_split, mode, partial, pstride, pld, error);
+  dim3 grid((rowsA + p.tile_rows - 1) / p.tile_rows, (rowsB + BN - 1) / BN, p.splits);
+  gemm_tc_kernel<BN, SWAP><<<grid, TC_THREADS, p.smem, s>>>(
+      tmA, tmB, C, c_dtype, ldc, rowsA, rowsB, K, p.kb_per_split, mode, partial, pstride, pld,
+      p.tile_rows, p.stages, p.a_stage, error);
   MB_CHECK_LAUNCH("mb_gemm_tc");
+}
+
+// Stages and shared memory for tiles of tile_rows x BN within `budget` bytes.
+static void plan_stages(TcPlan& p, int bn, int budget) {
+  p.a_stage = ((p.tile_rows + 7) / 8) * 8 * TC_BK * 2;
+  const int b_bytes = bn * TC_BK * 2;
+  const int fixed = 1024 /*alignment*/ + 1024 /*barriers*/ + (TC_A_TILE - p.a_stage);
+  int stages = (budget - fixed) / (p.a_stage + b_bytes);
+  if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
+  if (stages < 2) stages = 2;
+  p.stages = stages;
+  const int a_region = (stages - 1) * p.a_stage + TC_A_TILE;
+  p.smem = 1024 + a_region + stages * b_bytes + 1024;
 }
 
 // 1 if the sizes can go through mb_gemm_tc, else 0 with the reason in mb_last_error().
@@ -223,50 +282,84 @@ MB_EXPORT int mb_gemm_tc_supported(const void* A, int lda, const void* W, int M,
   return 1;
 }
 
-// C[M, N] (row stride ldc; bfloat16 or float32) = A[M, K] (row stride lda) · W[N, K]ᵀ, or
-// C += ... (epilogue 1, float32 C). `workspace` (float32, may be null) lets the K range be
-// split; `error` is a device word that receives a non-zero code if a wait in the kernel ran
-// out (1 load, 2 MMA, 3 epilogue). `sms`: the number of SMs of the device.
+// C[M, N] (row stride ldc; bfloat16 or float32) = A[M, K] (row stride lda) · W[N, K]ᵀ
+// (epilogue 0), C += ... (1, float32 C), or C[M, N / 2] = SwiGLU over a W whose rows alternate
+// gate and up (3, bfloat16 C). `workspace` (float32, may be null) lets the K range be split;
+// `error` is a device word that receives a non-zero code if a wait in the kernel ran out
+// (1 load, 2 MMA, 3 epilogue). `sms`: the number of SMs of the device.
 MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_dtype, int ldc,
                          int M, int N, int K, int epilogue, float* workspace,
                          long long workspace_floats, int* error, int sms, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!mb_gemm_tc_supported(A, lda, W, M, N, K)) return -1;
-  if (epilogue != TC_STORE && epilogue != TC_ADD) MB_FAIL("mb_gemm_tc: epilogue %d", epilogue);
+  if (epilogue != TC_STORE && epilogue != TC_ADD && epilogue != TC_SWIGLU)
+    MB_FAIL("mb_gemm_tc: epilogue %d", epilogue);
   if (epilogue == TC_ADD && c_dtype != MB_F32) MB_FAIL("mb_gemm_tc: the residual is float32");
+  if (epilogue == TC_SWIGLU && (c_dtype != MB_BF16 || (N & 1)))
+    MB_FAIL("mb_gemm_tc: SwiGLU writes bfloat16 from an even number of rows (%d)", N);
   cudaStream_t s = (cudaStream_t)stream;
   const bool swap = M <= 64;
   int bn;
   if (swap) bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   else bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
   const int rowsA = swap ? N : M, rowsB = swap ? M : N;
+  const int nkb = (K + TC_BK - 1) / TC_BK;
+  TcPlan p;
+  p.splits = 1;
+  p.kb_per_split = nkb;
+  if (swap) {
+    // Two CTAs share an SM (about half the shared memory each), so 2 * sms CTAs run at once.
+    // A weight with at least that many 128-row tiles streams tile by tile. One with fewer
+    // tiles than that, but more than sms, gets tiles of fewer rows so that one round of
+    // 2 * sms CTAs covers it evenly. One with at most sms tiles keeps its 128-row tiles (large
+    // TMA boxes) and splits K so that tiles * splits fills the 2 * sms places.
+    const int slots = 2 * sms;
+    const int tiles128 = (N + TC_BM - 1) / TC_BM;
+    int rows = TC_BM;
+    if (tiles128 > sms && tiles128 < slots) {
+      rows = (N + slots - 1) / slots;
+      rows += rows & 1;  // gate/up pairs stay in one tile
+    }
+    p.tile_rows = rows;
+    plan_stages(p, bn, 110 * 1024);
+    if (workspace && epilogue != TC_SWIGLU && tiles128 <= sms && nkb >= 8) {
+      int want = slots / tiles128;
+      if (want > nkb / 4) want = nkb / 4;
+      const long long per = (long long)M * N;
+      if (want > workspace_floats / per) want = (int)(workspace_floats / per);
+      if (want > 1) p.splits = want;
+    }
+    p.kb_per_split = (nkb + p.splits - 1) / p.splits;
+    p.splits = (nkb + p.kb_per_split - 1) / p.kb_per_split;
+  } else {
+    p.tile_rows = TC_BM;
+    plan_stages(p, bn, 200 * 1024);
+    const int tiles = ((rowsA + TC_BM - 1) / TC_BM) * ((rowsB + bn - 1) / bn);
+    if (workspace && epilogue != TC_SWIGLU && tiles < sms && nkb >= 8) {
+      int want = (2 * sms + tiles - 1) / tiles;
+      if (want > nkb / 4) want = nkb / 4;
+      const long long per = (long long)M * N;
+      if (want > workspace_floats / per) want = (int)(workspace_floats / per);
+      if (want > 1) p.splits = want;
+    }
+    p.kb_per_split = (nkb + p.splits - 1) / p.splits;
+    p.splits = (nkb + p.kb_per_split - 1) / p.kb_per_split;
+  }
   CUtensorMap tmA, tmB;
   if (swap) {
-    if (!mb_make_map_bf16(&tmA, W, N, K, K, TC_BM, "mb_gemm_tc weight")) return -1;
+    if (!mb_make_map_bf16(&tmA, W, N, K, K, p.tile_rows, "mb_gemm_tc weight")) return -1;
     if (!mb_make_map_bf16(&tmB, A, M, K, lda, bn, "mb_gemm_tc input")) return -1;
   } else {
     if (!mb_make_map_bf16(&tmA, A, M, K, lda, TC_BM, "mb_gemm_tc input")) return -1;
     if (!mb_make_map_bf16(&tmB, W, N, K, K, bn, "mb_gemm_tc weight")) return -1;
   }
-  const int tiles = ((rowsA + TC_BM - 1) / TC_BM) * ((rowsB + bn - 1) / bn);
-  const int nkb = (K + TC_BK - 1) / TC_BK;
-  int splits = 1;
-  if (workspace && tiles < sms && nkb >= 8) {
-    int want = (2 * sms + tiles - 1) / tiles;
-    if (want > nkb / 4) want = nkb / 4;
-    const long long per = (long long)M * N;
-    if (want > workspace_floats / per) want = (int)(workspace_floats / per);
-    if (want > 1) splits = want;
-  }
-  int per_split = (nkb + splits - 1) / splits;
-  splits = (nkb + per_split - 1) / per_split;
-  const int mode = splits > 1 ? TC_PARTIAL : epilogue;
-  float* partial = splits > 1 ? workspace : nullptr;
+  const int mode = p.splits > 1 ? TC_PARTIAL : epilogue;
+  float* partial = p.splits > 1 ? workspace : nullptr;
   const long long pstride = (long long)M * N, pld = N;
   int rc;
-#define GO(BN_, SW_)                                                                          \
-  rc = launch_tc<BN_, SW_>(tmA, tmB, C, c_dtype, ldc, rowsA, rowsB, K, splits, per_split, mode, \
-                           partial, pstride, pld, error, s)
+#define GO(BN_, SW_)                                                                        \
+  rc = launch_tc<BN_, SW_>(tmA, tmB, C, c_dtype, ldc, rowsA, rowsB, K, p, mode, partial,    \
+                           pstride, pld, error, s)
   if (swap) {
     if (bn == 16) GO(16, true); else if (bn == 32) GO(32, true); else GO(64, true);
   } else {
@@ -274,12 +367,12 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
   }
 #undef GO
   if (rc) return rc;
-  g_last_launches = splits > 1 ? 2 : 1;
-  if (splits > 1) {
+  g_last_launches = p.splits > 1 ? 2 : 1;
+  if (p.splits > 1) {
     const size_t total = (size_t)M * N;
     const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
-    splitk_reduce_kernel<<<blocks, 256, 0, s>>>(workspace, splits, pstride, C, c_dtype, ldc, M, N,
-                                                epilogue);
+    splitk_reduce_kernel<<<blocks, 256, 0, s>>>(workspace, p.splits, pstride, C, c_dtype, ldc, M,
+                                                N, epilogue);
     MB_CHECK_LAUNCH("mb_gemm_tc reduce");
   }
   return 0;

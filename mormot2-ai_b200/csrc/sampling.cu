@@ -72,12 +72,67 @@ argmax_kernel(const float* __restrict__ logits, size_t stride, int V, int* __res
   if (threadIdx.x == 0) out[blockIdx.x] = b.i;
 }
 
-// out[r] = arg-max of logits[r, 0..V)
+// Two stages for wide rows, so that more than one CTA a row reads the logits: every CTA of
+// the first stage finds the best of ARGMAX_CHUNK values, the second stage the best of those
+// (the lowest index still wins a tie: chunks are compared in order).
+#define ARGMAX_CHUNK 2048
+__global__ void __launch_bounds__(256)
+argmax_chunks_kernel(const float* __restrict__ logits, size_t stride, int V,
+                     Best* __restrict__ partial, int chunks) {
+  __shared__ Best sh[32];
+  const int i0 = blockIdx.x * ARGMAX_CHUNK;
+  const int n = min(ARGMAX_CHUNK, V - i0);
+  Best b = block_argmax(logits + blockIdx.y * stride + i0, n, sh);
+  if (threadIdx.x == 0) {
+    // an all-NaN chunk offers no candidate
+    const float v = logits[blockIdx.y * stride + i0 + b.i];
+    partial[(size_t)blockIdx.y * chunks + blockIdx.x] = Best{v, v != v ? -1 : i0 + b.i};
+  }
+}
+
+__global__ void __launch_bounds__(128)
+argmax_final_kernel(const Best* __restrict__ partial, int chunks, int* __restrict__ out) {
+  __shared__ Best sh[4];
+  Best b = {0.f, -1};
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    const Best x = partial[(size_t)blockIdx.x * chunks + c];
+    if (better(x, b)) b = x;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best c;
+    c.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+    c.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+    if (better(c, b)) b = c;
+  }
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = b;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 4; ++w)
+      if (better(sh[w], b)) b = sh[w];
+    out[blockIdx.x] = b.i < 0 ? 0 : b.i;
+  }
+}
+
+// bytes of scratch with which mb_argmax uses its two-stage form
+MB_EXPORT long long mb_argmax_scratch(int rows, int V) {
+  return (long long)rows * ((V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK) * (long long)sizeof(Best);
+}
+
+// out[r] = arg-max of logits[r, 0..V). `scratch` (may be null): mb_argmax_scratch bytes.
 MB_EXPORT int mb_argmax(const float* logits, long long stride, int rows, int V, int* out,
-                        void* stream) {
+                        void* scratch, long long scratch_bytes, void* stream) {
   if (rows <= 0) return 0;
   if (V <= 0) MB_FAIL("mb_argmax: a vocabulary of %d", V);
-  argmax_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, (size_t)stride, V, out);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int chunks = (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+  if (scratch && chunks > 4 && rows <= 65535 && scratch_bytes >= mb_argmax_scratch(rows, V)) {
+    argmax_chunks_kernel<<<dim3(chunks, rows), 256, 0, s>>>(logits, (size_t)stride, V,
+                                                           (Best*)scratch, chunks);
+    argmax_final_kernel<<<rows, 128, 0, s>>>((const Best*)scratch, chunks, out);
+  } else {
+    argmax_kernel<<<rows, SAMPLE_THREADS, 0, s>>>(logits, (size_t)stride, V, out);
+  }
   MB_CHECK_LAUNCH("mb_argmax");
 }
 

@@ -14,7 +14,7 @@ from .csrc import build
 from .errors import KernelError
 
 F32, BF16 = 0, 1
-EPI_STORE, EPI_ADD, EPI_SWIGLU = 0, 1, 2
+EPI_STORE, EPI_ADD, EPI_SWIGLU, EPI_SWIGLU_PAIRS = 0, 1, 2, 3
 PAGE = 64  # positions per cache page (MB_PAGE in csrc/common.cuh)
 
 _c = ctypes
@@ -135,10 +135,12 @@ def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, 
 
 # ------------------------------------------------------------------------------ products
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_STORE) -> None:
-    """c = a · wᵀ (store), c += a · wᵀ (add, float32 c), or SwiGLU over w = [gate; up]."""
+    """c = a · wᵀ (store), c += a · wᵀ (add, float32 c), or SwiGLU over w = [gate; up]
+    (EPI_SWIGLU) or over a w whose rows alternate gate, up (EPI_SWIGLU_PAIRS)."""
     M, K = a.shape
     N = c.shape[1]
-    assert w.shape[1] == K and w.shape[0] == (2 * N if epilogue == EPI_SWIGLU else N)
+    assert w.shape[1] == K
+    assert w.shape[0] == (2 * N if epilogue in (EPI_SWIGLU, EPI_SWIGLU_PAIRS) else N)
     assert c.shape[0] == M and a.stride(1) == 1 and c.stride(1) == 1
     _contig(w, "the weight")
     _call("gemm_simt", "mb_gemm_simt",
@@ -162,11 +164,16 @@ def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line
 
 
 # ------------------------------------------------------------------------------ sampling
-def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+def argmax(logits: torch.Tensor, out: torch.Tensor,
+           scratch: Optional[torch.Tensor] = None) -> None:
+    """out[r] = arg-max of row r; with ``scratch`` (8 bytes per row and 2048 values) wide rows
+    are read by many CTAs."""
     rows, V = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
-    _call("sampling", "mb_argmax", [_vp, _ll, _i, _i, _vp, _vp],
-          _ptr(logits), logits.stride(0), rows, V, _ptr(out), _stream())
+    nbytes = scratch.numel() * scratch.element_size() if scratch is not None else 0
+    _call("sampling", "mb_argmax", [_vp, _ll, _i, _i, _vp, _vp, _ll, _vp],
+          _ptr(logits), logits.stride(0), rows, V, _ptr(out), _ptr(scratch), nbytes, _stream(),
+          launches=2 if scratch is not None and V > 4 * 2048 else 1)
 
 
 def sample(logits: torch.Tensor, temperature: float, state_index: torch.Tensor,
@@ -190,18 +197,21 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, add: bool,
-            workspace: Optional[torch.Tensor], error: torch.Tensor, sms: int) -> None:
+            workspace: Optional[torch.Tensor], error: torch.Tensor, sms: int,
+            swiglu: bool = False) -> None:
     """c = a · wᵀ (or c += for a float32 c) with bfloat16 a [M, K] and w [N, K] on the tensor
-    cores. ``workspace``: float32 scratch for split sums; ``error``: int32 device word."""
+    cores; ``swiglu``: w's rows alternate gate and up and c [M, N / 2] = silu(gate) · up.
+    ``workspace``: float32 scratch for split sums; ``error``: int32 device word."""
     M, K = a.shape
     N = w.shape[0]
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
-    assert a.stride(1) == 1 and c.stride(1) == 1 and c.shape == (M, N)
+    assert a.stride(1) == 1 and c.stride(1) == 1 and c.shape == (M, N // 2 if swiglu else N)
     _contig(w, "the weight")
     _call("gemm_tc", "mb_gemm_tc",
           [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _ll, _vp, _i, _vp],
           _ptr(a), a.stride(0), _ptr(w), _ptr(c), code_of(c.dtype), c.stride(0), M, N, K,
-          1 if add else 0, _ptr(workspace), workspace.numel() if workspace is not None else 0,
+          3 if swiglu else (1 if add else 0), _ptr(workspace),
+          workspace.numel() if workspace is not None else 0,
           _ptr(error), sms, _stream())
     # the split of K adds one kernel that sums the partial products
     Launches.count += build.load_library("gemm_tc").mb_gemm_tc_last_launches() - 1

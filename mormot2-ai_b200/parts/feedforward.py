@@ -1,6 +1,7 @@
 """SwiGLU feed-forward: x += (silu(h·Wgᵀ) · (h·Wuᵀ)) · Wdᵀ, no bias
 (``decoder.pas:2865-2899``, ``backend.cpu.pas:1827-1833`` of the reference). Gate and up are
-one product whose epilogue applies the activation."""
+one product whose epilogue applies the activation: their rows are laid out alternately (gate
+of output 0, up of output 0, gate of output 1, ...), a pure re-layout done once at load."""
 from __future__ import annotations
 
 from typing import Dict, List
@@ -32,7 +33,8 @@ class SwiGluFfn(Part):
         g, u = weights[n["gate"]], weights[n["up"]]
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
-        self.gate_up = Linear(torch.cat([g, u], dim=0), rt, swiglu=True)
+        pairs = torch.stack([g, u], dim=1).reshape(2 * self.inter, self.hidden)
+        self.gate_up = Linear(pairs, rt, swiglu=True)
         self.down = Linear(weights[n["down"]], rt)
 
     def forward(self, h, x, step) -> None:

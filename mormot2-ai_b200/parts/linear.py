@@ -1,5 +1,5 @@
 """y = x · Wᵀ for a weight [out, in] without bias (``backend.pas:63-68`` of the reference),
-with the epilogue fused: store, add into the float32 residual, or SwiGLU over [gate; up].
+with the epilogue fused: store, add into the float32 residual, or SwiGLU over gate and up.
 
 The kernel is chosen by the operand types and sizes: the tensor-core kernels for bfloat16
 operands whose sizes they take, else the float32 multiply-add kernel, which takes every size
@@ -16,8 +16,9 @@ from .. import kernels as K
 
 class Linear:
     def __init__(self, weight: torch.Tensor, rt, swiglu: bool = False):
-        """``swiglu``: the weight is [gate; up] ([2 * out, in]) and the product is followed by
-        out = silu(gate) * up."""
+        """``swiglu``: the weight is [2 * out, in] with rows that alternate gate and up (row 2i
+        the gate, row 2i + 1 the up projection of output i) and the product is followed by
+        out = silu(gate) * up in the kernel's epilogue."""
         self.weight = weight.contiguous()
         self.rt = rt
         self.swiglu = swiglu
@@ -42,5 +43,5 @@ class Linear:
         if add_into is not None:
             K.gemm_simt(a, self.weight, add_into, K.EPI_ADD)
             return add_into
-        K.gemm_simt(a, self.weight, out, K.EPI_SWIGLU if self.swiglu else K.EPI_STORE)
+        K.gemm_simt(a, self.weight, out, K.EPI_SWIGLU_PAIRS if self.swiglu else K.EPI_STORE)
         return out

@@ -1,8 +1,7 @@
 """The tensor-core path of ``Linear``: bfloat16 operands through ``csrc/gemm_tc.cu``.
 
 Sizes that the kernel does not take (an inner size that is no multiple of 8, operands that
-are not 16-byte aligned) go back to the float32 multiply-add kernel. SwiGLU runs as the
-product over [gate; up] followed by the activation kernel.
+are not 16-byte aligned) go back to the float32 multiply-add kernel.
 """
 from __future__ import annotations
 
@@ -30,10 +29,7 @@ class FastLinear:
             return False
         rt = self.rt
         if self.swiglu:
-            gu = torch.empty((a.shape[0], self.weight.shape[0]), dtype=torch.bfloat16,
-                             device=a.device)
-            K.gemm_tc(a, self.weight, gu, False, rt.workspace, rt.error_word, rt.sms)
-            K.swiglu(gu, out)
+            K.gemm_tc(a, self.weight, out, False, rt.workspace, rt.error_word, rt.sms, swiglu=True)
             return True
         if add_into is not None:
             K.gemm_tc(a, self.weight, add_into, True, rt.workspace, rt.error_word, rt.sms)

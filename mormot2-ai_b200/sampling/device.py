@@ -15,6 +15,8 @@ class DeviceSampler:
     def __init__(self, device: torch.device, max_slots: int, vocab_size: int):
         self.device, self.vocab_size, self.max_slots = device, vocab_size, max_slots
         self.states = torch.zeros(max_slots, dtype=torch.int64, device=device)
+        self.argmax_scratch = torch.empty(max_slots * (vocab_size // 2048 + 1), dtype=torch.int64,
+                                          device=device)
         self.scratch: Optional[torch.Tensor] = None
         self.scratch_stride = 1
         while self.scratch_stride < vocab_size:
@@ -36,7 +38,7 @@ class DeviceSampler:
             logits = logits[:, :vocab_limit]
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
         if sampling.greedy:
-            K.argmax(logits, out)
+            K.argmax(logits, out, self.argmax_scratch if rows <= self.max_slots else None)
         elif not sampling.filtered:
             K.sample(logits, sampling.temperature, slots, self.states, out)
         else:

@@ -103,11 +103,15 @@ def test_gemm_simt(M, N, Kd, a_dt, w_dt, c_dt):
     K.gemm_simt(a.to(DEV), w2.to(DEV), c, K.EPI_SWIGLU)
     gu = (a.double() @ w2.double().T).float().numpy()
     assert rel(c.float().cpu(), plain.swiglu(gu[:, :N], gu[:, N:])) <= tol
+    c = torch.empty(M, N, dtype=DT[c_dt], device=DEV)         # rows alternating gate, up
+    K.gemm_simt(a.to(DEV), w2.to(DEV), c, K.EPI_SWIGLU_PAIRS)
+    assert rel(c.float().cpu(), plain.swiglu(gu[:, 0::2], gu[:, 1::2])) <= tol
 
 
 @pytest.mark.parametrize("M,N,Kd", [(1, 96, 64), (5, 509, 96), (16, 130, 328), (17, 256, 200),
                                     (64, 1000, 1024), (65, 77, 72), (128, 384, 192),
-                                    (300, 509, 320), (1030, 264, 520), (9, 4096, 2048)])
+                                    (300, 509, 320), (1030, 264, 520), (9, 4096, 2048),
+                                    (8, 19000, 256), (40, 40000, 128), (3, 150, 64)])
 def test_gemm_tensor_cores(rt, M, N, Kd):
     """Both orientations of csrc/gemm_tc.cu (tokens or weight rows on the TMEM lanes), tails in
     every dimension, the split of K, all epilogues."""
@@ -126,6 +130,11 @@ def test_gemm_tensor_cores(rt, M, N, Kd):
     c = r.to(DEV)                                                 # without scratch: no split
     K.gemm_tc(a.to(DEV), w.to(DEV), c, True, None, rt.error_word, rt.sms)
     assert rel(c.cpu(), want + r.double()) <= 2e-5
+    if N % 2 == 0:                                # SwiGLU over rows that alternate gate, up
+        c = torch.full((M, N // 2), 3.0, dtype=torch.bfloat16, device=DEV)
+        K.gemm_tc(a.to(DEV), w.to(DEV), c, False, rt.workspace, rt.error_word, rt.sms, swiglu=True)
+        y = want.float().numpy()
+        assert rel(c.float().cpu(), plain.swiglu(y[:, 0::2], y[:, 1::2])) <= 8e-3
     rt.check()
 
 
@@ -320,6 +329,15 @@ def test_argmax_ties_nan_and_wide_rows():
     K.argmax(view, out)
     want = [plain.arg_max(r.numpy()) for r in big[:, :151936 + 3]]
     assert out.tolist() == want and want[2] == 77
+    # the two-stage form: ties across chunks, a chunk of NaN only, the last short chunk
+    big[3, 4096:6144] = float("nan")
+    big[4, :] = float("nan")
+    big[5, 151936 + 2] = 50.0
+    want = [plain.arg_max(r.numpy()) for r in big[:, :151936 + 3]]
+    scratch = torch.empty(6 * 80, dtype=torch.int64, device=DEV)
+    out.fill_(-1)
+    K.argmax(big.to(DEV)[:, :151936 + 3], out, scratch)
+    assert out.tolist() == want and want[2] == 77 and want[4] == 0 and want[5] == 151936 + 2
 
 
 @pytest.mark.parametrize("settings", [dict(temperature=1.0), dict(temperature=0.7),
