@@ -130,6 +130,14 @@ def compile_library(name: str, verbose: bool = True) -> str:
             pass
         raise KernelError(f"nvcc failed on {SOURCES[name]}:\n{log.decode(errors='replace')}")
     os.replace(tmp, out)
+    # builds of older sources of this library are of no use any more
+    prefix = f"libmb_{name}-"
+    for fn in os.listdir(os.path.dirname(out)):
+        if fn.startswith(prefix) and fn.endswith(".so") and fn != os.path.basename(out):
+            try:
+                os.unlink(os.path.join(os.path.dirname(out), fn))
+            except OSError:
+                pass
     if verbose:
         print(f"[mormot2-ai_b200] compiled {SOURCES[name]} in {time.time() - t0:.1f} s",
               file=sys.stderr, flush=True)

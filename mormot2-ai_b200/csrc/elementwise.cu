@@ -76,10 +76,82 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
   }
 }
 
+
+// The same for rows of 4 * RMS_THREADS * VEC values at most (a multiple of 4): the row is read
+// once with 16-byte loads, kept in registers, and written with 8- or 16-byte stores.
+#define RMS_THREADS 256
+template <typename TW, typename TO, int VEC>
+__global__ void __launch_bounds__(RMS_THREADS)
+rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partial, int parts,
+                   size_t part_stride, const TW* __restrict__ w, float eps, TO* __restrict__ y,
+                   const int* __restrict__ rows, int H) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* xr = x + (size_t)src * H;
+  float4 v[VEC];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int c = (i * RMS_THREADS + threadIdx.x) * 4;
+    v[i] = c < H ? *(const float4*)(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (parts > 0) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = (i * RMS_THREADS + threadIdx.x) * 4;
+      if (c >= H) continue;
+      for (int p = 0; p < parts; ++p) {
+        const float4 a = *(const float4*)(partial + p * part_stride + (size_t)src * H + c);
+        v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
+      }
+      *(float4*)(xr + c) = v[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VEC; ++i)
+    sum = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, sum))));
+  sum = block_sum(sum, red);
+  if (y == nullptr) return;
+  const float inv = 1.0f / sqrtf(sum / (float)H + eps);
+  TO* yr = y + (size_t)r * H;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int c = (i * RMS_THREADS + threadIdx.x) * 4;
+    if (c >= H) continue;
+    float o[4];
+    o[0] = to_f32<TW>(w[c]) * (v[i].x * inv);
+    o[1] = to_f32<TW>(w[c + 1]) * (v[i].y * inv);
+    o[2] = to_f32<TW>(w[c + 2]) * (v[i].z * inv);
+    o[3] = to_f32<TW>(w[c + 3]) * (v[i].w * inv);
+    if (sizeof(TO) == 4) {
+      *(float4*)((float*)yr + c) = make_float4(o[0], o[1], o[2], o[3]);
+    } else {
+      __nv_bfloat162 h[2] = {__floats2bfloat162_rn(o[0], o[1]), __floats2bfloat162_rn(o[2], o[3])};
+      *(uint2*)((__nv_bfloat16*)yr + c) = *(uint2*)h;
+    }
+  }
+}
+
 template <typename TW, typename TO>
 static int rmsnorm_launch(float* x, const float* partial, int parts, size_t part_stride,
                           const void* w, float eps, void* y, const int* rows, int R, int H,
                           cudaStream_t s) {
+  const bool aligned = ((uintptr_t)x & 15) == 0 && ((uintptr_t)partial & 15) == 0 &&
+                       (part_stride & 3) == 0 && ((uintptr_t)y & 15) == 0;
+  if (H % 4 == 0 && H <= 4 * RMS_THREADS * 16 && aligned) {
+    const int vec = (H + 4 * RMS_THREADS - 1) / (4 * RMS_THREADS);
+#define RMS_GO(V_)                                                                          \
+  rmsnorm_vec_kernel<TW, TO, V_><<<R, RMS_THREADS, 0, s>>>(x, partial, parts, part_stride,     \
+                                                           (const TW*)w, eps, (TO*)y, rows, H)
+    if (vec <= 1) RMS_GO(1);
+    else if (vec <= 2) RMS_GO(2);
+    else if (vec <= 4) RMS_GO(4);
+    else if (vec <= 8) RMS_GO(8);
+    else RMS_GO(16);
+#undef RMS_GO
+    MB_CHECK_LAUNCH("mb_rmsnorm");
+  }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   const size_t smem = parts > 0 ? (size_t)H * sizeof(float) : 0;
   if (smem > 48 * 1024) {
@@ -200,7 +272,98 @@ __global__ void qk_norm_rope_store_kernel(
   }
 }
 
-MB_EXPORT int mb_qk_norm_rope_store(void* qkv, int dtype, const void* q_norm, const void* k_norm,
+
+// The same for bfloat16 heads of 64, 128 or 256 values that rotate as a whole: one warp per
+// (token, head), every lane holds V = hd / 64 neighbouring values of the first half and their
+// rotation partners of the second half, so nothing goes through shared memory. The source is
+// the fused qkv row, or (PARTIAL) the float32 partial sums of a split product
+// [parts][T][width], which are added up here in split order. q goes to q_out [T, nh * hd] when
+// given, else back in place.
+template <int V, typename TW, bool PARTIAL>
+__global__ void __launch_bounds__(QK_WARPS * 32)
+qk_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partial, int parts,
+               size_t part_stride, __nv_bfloat16* __restrict__ q_out,
+               const TW* __restrict__ q_norm, const TW* __restrict__ k_norm, float eps,
+               const float* __restrict__ inv_freq, const int* __restrict__ tok_seq,
+               const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
+               const int* __restrict__ page_table, int max_pages, int ring_pages,
+               __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int nh,
+               int nkv, int write_kv) {
+  constexpr int HD = 64 * V, HALF = 32 * V;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int head = blockIdx.y * QK_WARPS + warp;
+  const int total = nh + 2 * nkv;
+  if (head >= total) return;
+  const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+  if (!is_q && !write_kv) return;
+  const size_t col = (size_t)head * HD + V * lane;
+  float a[V], b[V];
+  if (PARTIAL) {
+#pragma unroll
+    for (int j = 0; j < V; ++j) a[j] = b[j] = 0.f;
+    for (int p = 0; p < parts; ++p) {
+      const float* src = partial + p * part_stride + (size_t)t * total * HD + col;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        a[j] += src[j];
+        b[j] += src[HALF + j];
+      }
+    }
+  } else {
+    const __nv_bfloat16* src = qkv + (size_t)t * total * HD + col;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      a[j] = __bfloat162float(src[j]);
+      b[j] = __bfloat162float(src[HALF + j]);
+    }
+  }
+  const int pos = tok_pos[t];
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = q_out ? q_out + (size_t)t * nh * HD + col : qkv + (size_t)t * total * HD + col;
+  } else {
+    const int g = is_k ? head - nh : head - nh - nkv;
+    const size_t row = kv_row(page_table, max_pages, ring_pages, seq_slot[tok_seq[t]], pos, nkv, g);
+    dst = (is_k ? kpool : vpool) + row * HD + V * lane;
+  }
+  if (is_q || is_k) {
+    const TW* w = is_q ? q_norm : k_norm;
+    if (w) {
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < V; ++j) sum = fmaf(a[j], a[j], fmaf(b[j], b[j], sum));
+      sum = warp_sum(sum);
+      const float inv = 1.0f / sqrtf(sum / (float)HD + eps);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        a[j] = to_f32<TW>(w[V * lane + j]) * (a[j] * inv);
+        b[j] = to_f32<TW>(w[HALF + V * lane + j]) * (b[j] * inv);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float angle = inv_freq[V * lane + j] * (float)pos;  // float32 product
+      float sn, cs;
+      sincosf(angle, &sn, &cs);
+      const float ra = a[j] * cs - b[j] * sn, rb = b[j] * cs + a[j] * sn;
+      a[j] = ra;
+      b[j] = rb;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    dst[j] = __float2bfloat16_rn(a[j]);
+    dst[HALF + j] = __float2bfloat16_rn(b[j]);
+  }
+}
+
+// `partial` (may be null): float32 [parts][T][(nh + 2 nkv) hd] partial sums that stand for qkv
+// (bfloat16 heads of 64/128/256 values that rotate as a whole only); `q_out` (may be null):
+// where q goes instead of back into qkv, [T, nh * hd].
+MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
+                                    long long part_stride, void* q_out, int dtype,
+                                    const void* q_norm, const void* k_norm,
                                     int w_dtype, float eps, const float* inv_freq, int rot_dim,
                                     const int* tok_seq, const int* tok_pos, const int* seq_slot,
                                     const int* page_table, int max_pages, int ring_pages,
@@ -212,6 +375,25 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, int dtype, const void* q_norm, co
   if (hd <= 0 || hd > 1024) MB_FAIL("mb_qk_norm_rope_store: heads of %d", hd);
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(T, (nh + 2 * nkv + QK_WARPS - 1) / QK_WARPS);
+  const bool fast = dtype == MB_BF16 && rot_dim == hd && (hd == 64 || hd == 128 || hd == 256);
+  if ((partial || q_out) && !fast)
+    MB_FAIL("mb_qk_norm_rope_store: partial sums or a separate q for heads of %d values "
+            "(%d rotate) are not supported", hd, rot_dim);
+  if (fast) {
+    typedef __nv_bfloat16 bf;
+#define QKF(V_, TW_, P_)                                                                       \
+  qk_fast_kernel<V_, TW_, P_><<<grid, QK_WARPS * 32, 0, s>>>(                                   \
+      (bf*)qkv, partial, parts, (size_t)part_stride, (bf*)q_out, (const TW_*)q_norm,           \
+      (const TW_*)k_norm, eps, inv_freq, tok_seq, tok_pos, seq_slot, page_table, max_pages,    \
+      ring_pages, (bf*)kpool, (bf*)vpool, nh, nkv, write_kv)
+#define QKF_V(TW_, P_)                                                                         \
+  if (hd == 64) QKF(1, TW_, P_); else if (hd == 128) QKF(2, TW_, P_); else QKF(4, TW_, P_)
+    if (w_dtype == MB_F32) { if (partial) { QKF_V(float, true); } else { QKF_V(float, false); } }
+    else { if (partial) { QKF_V(bf, true); } else { QKF_V(bf, false); } }
+#undef QKF_V
+#undef QKF
+    MB_CHECK_LAUNCH("mb_qk_norm_rope_store");
+  }
   const size_t smem = (size_t)QK_WARPS * hd * sizeof(float);
 #define QK_LAUNCH(T_, TW_)                                                                     \
   qk_norm_rope_store_kernel<T_, TW_><<<grid, QK_WARPS * 32, smem, s>>>(                        \

@@ -27,6 +27,10 @@
 MB_DEFINE_LAST_ERROR
 
 static thread_local int g_last_launches = 0;
+static thread_local int g_last_splits = 1;
+// splits of K in the last mb_gemm_tc of this thread; with `defer` and more than one split the
+// partial sums [splits][M][N] were left in the workspace for the caller's next kernel to add
+MB_EXPORT int mb_gemm_tc_last_splits() { return g_last_splits; }
 // kernels that the last mb_gemm_tc of this thread launched (2 when K was split)
 MB_EXPORT int mb_gemm_tc_last_launches() { return g_last_launches; }
 
@@ -286,10 +290,14 @@ MB_EXPORT int mb_gemm_tc_supported(const void* A, int lda, const void* W, int M,
 // (epilogue 0), C += ... (1, float32 C), or C[M, N / 2] = SwiGLU over a W whose rows alternate
 // gate and up (3, bfloat16 C). `workspace` (float32, may be null) lets the K range be split;
 // `error` is a device word that receives a non-zero code if a wait in the kernel ran out
-// (1 load, 2 MMA, 3 epilogue). `sms`: the number of SMs of the device.
+// (1 load, 2 MMA, 3 epilogue). `sms`: the number of SMs of the device. `defer`: when K was split
+// (mb_gemm_tc_last_splits() > 1) the partial sums stay in the workspace as [splits][M][N] and C
+// is not touched: the caller's next kernel adds them up.
 MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_dtype, int ldc,
                          int M, int N, int K, int epilogue, float* workspace,
-                         long long workspace_floats, int* error, int sms, void* stream) {
+                         long long workspace_floats, int defer, int* error, int sms,
+                         void* stream) {
+  g_last_splits = 1;
   if (M <= 0 || N <= 0) return 0;
   if (!mb_gemm_tc_supported(A, lda, W, M, N, K)) return -1;
   if (epilogue != TC_STORE && epilogue != TC_ADD && epilogue != TC_SWIGLU)
@@ -367,8 +375,9 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
   }
 #undef GO
   if (rc) return rc;
-  g_last_launches = p.splits > 1 ? 2 : 1;
-  if (p.splits > 1) {
+  g_last_launches = (p.splits > 1 && !defer) ? 2 : 1;
+  g_last_splits = p.splits;
+  if (p.splits > 1 && !defer) {
     const size_t total = (size_t)M * N;
     const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
     splitk_reduce_kernel<<<blocks, 256, 0, s>>>(workspace, p.splits, pstride, C, c_dtype, ldc, M,

@@ -15,6 +15,7 @@ from ..config.spec import ModelSpec
 from ..errors import ConfigError
 from ..parts import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS
 from ..parts.base import CacheNeed, StateNeed, TensorNeed
+from ..parts.block import settle
 
 
 class Layer:
@@ -112,12 +113,25 @@ class DecoderModel:
         self.embedding.forward(step.tok_ids, x)
         if on_state:
             on_state("embed", x)
+        pending = None      # split sums of the last product, not yet added into x
         for i, run in enumerate(self.spec.schedule):
             line = cache.lines.get(run.cache_line) if run.cache_line is not None else None
             state = cache.states.get(run.cache_line) if run.cache_line is not None else None
-            self.layers[run.layer].block.forward(x, step, line, state, run.writes_cache)
+            block = self.layers[run.layer].block
+            if getattr(block, "accepts_pending", False):
+                pending = block.forward(x, step, line, state, run.writes_cache, pending=pending)
+            else:
+                if pending is not None:
+                    settle(x, pending)
+                pending = None
+                block.forward(x, step, line, state, run.writes_cache)
             if on_state:
+                if pending is not None:
+                    settle(x, pending)
+                    pending = None
                 on_state(f"run{i:02d}", x)
+        if pending is not None:
+            settle(x, pending)
         if step.n_want == 0:
             return None
         h = self.final_norm.forward(x, rows=step.want_rows, n_rows=step.n_want)

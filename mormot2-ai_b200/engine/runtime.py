@@ -23,6 +23,9 @@ class Runtime:
         # one of their bounded waits ran out
         self.workspace = (torch.empty(16 << 20, dtype=torch.float32, device=self.device)
                           if self.fast_kernels else None)
+        # the partial sums of a split product that its consumer adds up (parts/linear.py)
+        self.pending_buf = (torch.empty(8 << 20, dtype=torch.float32, device=self.device)
+                            if self.fast_kernels else None)
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     def check(self) -> None:

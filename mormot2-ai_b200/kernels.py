@@ -101,6 +101,17 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Te
           _ptr(out), code_of(out.dtype) if out is not None else F32, _ptr(rows), R, H, _stream())
 
 
+def add_partials(x: torch.Tensor, partial: torch.Tensor) -> None:
+    """x += partial[0] + partial[1] + ... (float32 [parts, T, H]), in that order."""
+    assert x.dtype == torch.float32 and partial.dtype == torch.float32 and partial.is_contiguous()
+    _contig(x, "x")
+    T, H = x.shape
+    _call("elementwise", "mb_rmsnorm",
+          [_vp, _vp, _i, _ll, _vp, _i, _f, _vp, _i, _vp, _i, _i, _vp],
+          _ptr(x), _ptr(partial), partial.shape[0], partial.stride(0), None, F32, 0.0, None, F32,
+          None, T, H, _stream())
+
+
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     """out[T, I] = silu(gate_up[:, :I]) * gate_up[:, I:]."""
     T, I = out.shape
@@ -111,11 +122,20 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, nh, nkv, hd,
-                       write_kv: bool) -> None:
-    """Per-head norm of q and k, rotary positions, q in place, k and v into the cache line."""
-    T = qkv.shape[0]
-    _contig(qkv, "qkv")
-    assert qkv.shape[1] == (nh + 2 * nkv) * hd
+                       write_kv: bool, partial: Optional[torch.Tensor] = None,
+                       q_out: Optional[torch.Tensor] = None) -> None:
+    """Per-head norm of q and k, rotary positions, q in place (or into ``q_out``), k and v into
+    the cache line. ``partial`` [parts, T, width] float32: the split sums of the q/k/v product,
+    which stand for ``qkv`` (then None) and are added up here."""
+    if partial is not None:
+        assert partial.dtype == torch.float32 and partial.is_contiguous() and q_out is not None
+        T, width = partial.shape[1], partial.shape[2]
+        dtype_code = code_of(q_out.dtype)
+    else:
+        T, width = qkv.shape
+        _contig(qkv, "qkv")
+        dtype_code = code_of(qkv.dtype)
+    assert width == (nh + 2 * nkv) * hd
     if rot_dim > 0 and inv_freq is None:
         raise KernelError("a rotary encoding without its frequencies (is the position "
                           "encoding bound?)")
@@ -125,9 +145,11 @@ def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, 
         raise KernelError("q_norm and k_norm come together")
     wd = code_of(q_norm.dtype) if q_norm is not None else F32
     _call("elementwise", "mb_qk_norm_rope_store",
-          [_vp, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp,
-           _i, _i, _i, _i, _i, _vp],
-          _ptr(qkv), code_of(qkv.dtype), _ptr(q_norm), _ptr(k_norm), wd, float(eps),
+          [_vp, _vp, _i, _ll, _vp, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _vp, _vp, _i, _i,
+           _vp, _vp, _i, _i, _i, _i, _i, _vp],
+          _ptr(qkv), _ptr(partial), partial.shape[0] if partial is not None else 0,
+          partial.stride(0) if partial is not None else 0, _ptr(q_out), dtype_code,
+          _ptr(q_norm), _ptr(k_norm), wd, float(eps),
           _ptr(inv_freq), rot_dim, _ptr(step.tok_seq), _ptr(step.tok_pos), _ptr(step.seq_slot),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(line.k), _ptr(line.v),
           T, nh, nkv, hd, 1 if write_kv else 0, _stream())
@@ -198,23 +220,27 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, add: bool,
             workspace: Optional[torch.Tensor], error: torch.Tensor, sms: int,
-            swiglu: bool = False) -> None:
+            swiglu: bool = False, defer: bool = False) -> int:
     """c = a · wᵀ (or c += for a float32 c) with bfloat16 a [M, K] and w [N, K] on the tensor
     cores; ``swiglu``: w's rows alternate gate and up and c [M, N / 2] = silu(gate) · up.
-    ``workspace``: float32 scratch for split sums; ``error``: int32 device word."""
+    ``workspace``: float32 scratch for split sums; ``error``: int32 device word. ``defer``:
+    when K was split (the return value, the number of splits, is above 1) the partial sums stay
+    in the workspace as [splits, M, N] and c is not touched."""
     M, K = a.shape
     N = w.shape[0]
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
     assert a.stride(1) == 1 and c.stride(1) == 1 and c.shape == (M, N // 2 if swiglu else N)
     _contig(w, "the weight")
     _call("gemm_tc", "mb_gemm_tc",
-          [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _ll, _vp, _i, _vp],
+          [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _ll, _i, _vp, _i, _vp],
           _ptr(a), a.stride(0), _ptr(w), _ptr(c), code_of(c.dtype), c.stride(0), M, N, K,
           3 if swiglu else (1 if add else 0), _ptr(workspace),
-          workspace.numel() if workspace is not None else 0,
+          workspace.numel() if workspace is not None else 0, 1 if defer else 0,
           _ptr(error), sms, _stream())
     # the split of K adds one kernel that sums the partial products
-    Launches.count += build.load_library("gemm_tc").mb_gemm_tc_last_launches() - 1
+    lib = build.load_library("gemm_tc")
+    Launches.count += lib.mb_gemm_tc_last_launches() - 1
+    return lib.mb_gemm_tc_last_splits()
 
 
 def advance_decode(tok_ids: torch.Tensor, tok_pos: torch.Tensor, chosen: torch.Tensor,

@@ -71,11 +71,32 @@ class GqaAttention(Part):
         self.q_norm = weights.get(n.get("q_norm", ""))
         self.k_norm = weights.get(n.get("k_norm", ""))
 
-    def forward(self, h, x, step, line, state, writes_cache: bool) -> None:
+    def forward(self, h, x, step, line, state, writes_cache: bool):
+        """Adds the mixer's output into x, or returns it as ``Pending`` split sums for the next
+        norm to add (a decode step whose output product splits K)."""
+        from .linear import Pending
         T = h.shape[0]
         nkv = self.nkv if writes_cache else 0
         width = self.qw + 2 * nkv * self.hd
-        if not writes_cache:
+        eps = float(self.head_norm_eps) if self.head_norm_eps is not None else 0.0
+        inv_freq, rot_dim = (self.position.frequencies() if self.position is not None
+                             else (None, 0))
+        split_ok = (writes_cache and self.qkv is not None and rot_dim == self.hd
+                    and self.hd in (64, 128, 256) and self.rt.dtype == torch.bfloat16)
+        qkv = self.qkv(h, defer=True) if split_ok else None
+        if isinstance(qkv, Pending):
+            # the kernel that norms and rotates q and k adds the split sums up as it reads them
+            q = torch.empty((T, self.qw), dtype=self.rt.dtype, device=h.device)
+            K.qk_norm_rope_store(None, self.q_norm, self.k_norm, eps, inv_freq, rot_dim, step,
+                                 line, self.nh, nkv, self.hd, True, partial=qkv.partial, q_out=q)
+            attn = torch.empty((T, self.qw), dtype=self.rt.dtype, device=h.device)
+            self.rt.attention(q, self.qw, attn, step, line, self.nh, self.nkv, self.hd,
+                              self.window, self.scale)
+            out = self.o(attn, add_into=x, defer=True)
+            return out if isinstance(out, Pending) else None
+        if qkv is not None:
+            pass
+        elif not writes_cache:
             qkv = self.q_only(h)
         elif self.qkv is not None:
             qkv = self.qkv(h)
@@ -84,15 +105,13 @@ class GqaAttention(Part):
             self.split[0](h, out=qkv[:, :self.qw])
             self.split[1](h, out=qkv[:, self.qw:self.qw + self.kvw])
             self.split[2](h, out=qkv[:, self.qw + self.kvw:])
-        eps = float(self.head_norm_eps) if self.head_norm_eps is not None else 0.0
-        inv_freq, rot_dim = (self.position.frequencies() if self.position is not None
-                             else (None, 0))
         K.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, eps, inv_freq, rot_dim,
                              step, line, self.nh, nkv, self.hd, writes_cache)
         attn = torch.empty((T, self.qw), dtype=self.rt.dtype, device=h.device)
         self.rt.attention(qkv, width, attn, step, line, self.nh, self.nkv, self.hd,
                           self.window, self.scale)
-        self.o(attn, add_into=x)
+        out = self.o(attn, add_into=x, defer=True)
+        return out if isinstance(out, Pending) else None
 
 
 MIXERS.register("gqa_attention", GqaAttention)

@@ -15,12 +15,15 @@ position, in which slot):
 - Norm:      ``forward(x_f32[T, size], rows=None) -> h[R, size]`` in the activation dtype.
 - Position:  ``frequencies() -> (inv_freq_f32[rot_dim/2] on the device, rot_dim)``.
 - Mixer:     ``forward(h[T, hidden], x_f32[T, hidden], step, line, state, writes_cache)``:
-             adds its output to the residual ``x`` in place. ``line`` is the view of its
-             cache line (``cache/storage.py``), ``state`` its per-sequence state
-             ``[slots, *shape]`` or None.
-- FeedForward: ``forward(h[T, hidden], x_f32[T, hidden], step)``: adds into ``x``.
+             adds its output to the residual ``x`` in place and returns None. ``line`` is the
+             view of its cache line (``cache/storage.py``), ``state`` its per-sequence state
+             ``[slots, *shape]`` or None. (A built-in part may instead return its output as
+             ``Pending`` split sums, ``parts/linear.py``, which the next norm adds into x.)
+- FeedForward: ``forward(h[T, hidden], x_f32[T, hidden], step)``: adds into ``x``, returns None
+             (or ``Pending``, as above).
 - Block:     ``forward(x_f32, step, line, state, writes_cache)``: arranges norms, mixer and
-             feed-forward around the residual stream.
+             feed-forward around the residual stream. A block with ``accepts_pending = True``
+             also takes ``pending=`` (sums that the block before left) and returns its own.
 """
 from __future__ import annotations
 

@@ -37,9 +37,13 @@ class SwiGluFfn(Part):
         self.gate_up = Linear(pairs, rt, swiglu=True)
         self.down = Linear(weights[n["down"]], rt)
 
-    def forward(self, h, x, step) -> None:
+    def forward(self, h, x, step):
+        """Adds the feed-forward's output into x, or returns it as ``Pending`` split sums for
+        the next norm to add."""
+        from .linear import Pending
         act = self.gate_up(h)
-        self.down(act, add_into=x)
+        out = self.down(act, add_into=x, defer=True)
+        return out if isinstance(out, Pending) else None
 
 
 FEED_FORWARDS.register("swiglu", SwiGluFfn)

@@ -14,6 +14,16 @@ import torch
 from .. import kernels as K
 
 
+class Pending:
+    """Partial sums [splits, M, N] (float32) of a product whose K range was split: whoever
+    reads the result next adds them up, in split order (an RMSNorm adds them into the residual
+    it norms, the q/k norm kernel adds them as it reads q, k and v). They live in one buffer of
+    the runtime, so at most one product is pending at a time."""
+
+    def __init__(self, partial: torch.Tensor):
+        self.partial = partial
+
+
 class Linear:
     def __init__(self, weight: torch.Tensor, rt, swiglu: bool = False):
         """``swiglu``: the weight is [2 * out, in] with rows that alternate gate and up (row 2i
@@ -31,10 +41,16 @@ class Linear:
 
     def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor] = None,
                  add_into: Optional[torch.Tensor] = None,
-                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                 out_dtype: Optional[torch.dtype] = None, defer: bool = False):
         """``add_into``: the float32 residual [M, out] that the product is added to (returned).
-        Otherwise the product (or its SwiGLU) is stored in ``out`` (made if None)."""
+        Otherwise the product (or its SwiGLU) is stored in ``out`` (made if None). ``defer``: if
+        the kernel splits K, a ``Pending`` with the partial sums is returned instead and neither
+        ``out`` nor ``add_into`` is touched."""
         M = a.shape[0]
+        if self.fast is not None and defer and not self.swiglu:
+            pending = self.fast.deferred(a)
+            if pending is not None:
+                return pending
         if add_into is None and out is None:
             out = torch.empty((M, self.out_features), dtype=out_dtype or self.rt.dtype,
                               device=a.device)

@@ -22,6 +22,23 @@ class FastLinear:
             return None
         return cls(weight, rt, swiglu)
 
+    def deferred(self, a: torch.Tensor):
+        """The product with its split sums left pending, or None if this call does not split
+        (few tokens and a weight with few row tiles split; see csrc/gemm_tc.cu)."""
+        from .linear import Pending
+        rt = self.rt
+        M, N = a.shape[0], self.weight.shape[0]
+        if (a.dtype != torch.bfloat16 or a.stride(0) % 8 or a.data_ptr() % 16 or M > 64
+                or -(-N // 128) > rt.sms or rt.pending_buf is None):
+            return None
+        # c is only written when the kernel does not split after all
+        c = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        splits = K.gemm_tc(a, self.weight, c, False, rt.pending_buf, rt.error_word, rt.sms,
+                           defer=True)
+        if splits <= 1:
+            return Pending(c.unsqueeze(0))
+        return Pending(rt.pending_buf[:splits * M * N].view(splits, M, N))
+
     def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor],
                  add_into: Optional[torch.Tensor]) -> bool:
         """True if the product was done here."""

@@ -28,13 +28,14 @@ class RmsNorm(Part):
         self.rt = rt
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None,
-                n_rows: Optional[int] = None,
-                partial: Optional[torch.Tensor] = None) -> torch.Tensor:
+                n_rows: Optional[int] = None, pending=None) -> torch.Tensor:
         """x: the float32 residual [T, size]. ``rows``: only these rows are normed (gathered).
-        ``partial`` [parts, T, size]: split results that are first added into x."""
+        ``pending``: the split sums of the product before (``parts/linear.py: Pending``), which
+        are first added into x."""
         R = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
         out = torch.empty((R, self.size), dtype=self.rt.dtype, device=x.device)
-        K.rmsnorm(x, self.weight, self.eps, out, rows, R, partial)
+        K.rmsnorm(x, self.weight, self.eps, out, rows, R,
+                  pending.partial if pending is not None else None)
         return out
 
 
