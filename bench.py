@@ -204,6 +204,7 @@ def main():
     ap.add_argument("--layers", type=int, default=36, help="fewer layers than the 36 of the shape "
                     "(named in config); the layer sizes stay")
     ap.add_argument("--skip-points", action="store_true", help="no batch 1 / 64 / prefill runs")
+    ap.add_argument("--batches", default="1,64", help="batch sizes of the extra decode points")
     ap.add_argument("--only-prefill", action="store_true",
                     help="only the 2,048-token prefill (for profiles; prints its own short line)")
     a = ap.parse_args()
@@ -271,7 +272,7 @@ def main():
                           "ms": round(pms, 3),
                           "frac": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
         points = {}
-        for b in (1, 64):
+        for b in [int(v) for v in a.batches.split(',') if v]:
             steps = min(a.steps, 128)
             bms, _, _ = timed_decode(torch, eng, sampler, greedy, b, steps, a.warmup, 10 + b)
             points[f"decode_b{b}"] = round(b * steps / (bms / 1e3), 1)

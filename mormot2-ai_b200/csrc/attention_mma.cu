@@ -90,6 +90,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const int* __restrict__ tok_pos, const int* __restrict__ seq_slot, int nh,
                    int nkv, int window, float scale_log2, int pages_per_split,
                    float* __restrict__ part_o, float* __restrict__ part_ml) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   constexpr int CH = HD / 32;  // 32-dim chunks of q·k
   constexpr int DB = HD / 64;  // 64-dim blocks of p·v
   __shared__ float sm_m[DEC_WARPS][16], sm_l[DEC_WARPS][16];
@@ -231,6 +233,8 @@ template <int HD>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o,
                                   const float* __restrict__ part_ml, int S, bf16* __restrict__ out,
                                   int out_stride, int nh) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const size_t at = ((size_t)t * nh + h) * S;
   float M = -INFINITY;
@@ -281,11 +285,11 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(splits, nkv * subs, T), mgrid(T, nh);
 #define GO(HD_)                                                                                \
-  attn_decode_kernel<HD_><<<grid, DEC_WARPS * 32, 0, s>>>(                                      \
+  mb_launch(attn_decode_kernel<HD_>, dim3(grid), dim3(DEC_WARPS * 32), 0, s,                                       \
       (const bf16*)q, q_stride, (const bf16*)kpool, (const bf16*)vpool, page_table, max_pages, \
       ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, window, scale_log2, pages_per_split,    \
       part_o, part_ml);                                                                        \
-  attn_merge_kernel<HD_><<<mgrid, HD_, 0, s>>>(part_o, part_ml, splits, (bf16*)out, out_stride, nh)
+  mb_launch(attn_merge_kernel<HD_>, dim3(mgrid), dim3(HD_), 0, s, part_o, part_ml, splits, (bf16*)out, out_stride, nh)
   if (hd == 64) { GO(64); } else { GO(128); }
 #undef GO
   MB_CHECK_LAUNCH("mb_attention_decode");
@@ -305,6 +309,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
                     int max_pages, int ring_pages, const int* __restrict__ seq_start,
                     const int* __restrict__ seq_past, const int* __restrict__ seq_slot, int nh,
                     int nkv, int window, float scale_log2) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   constexpr int CH = HD / 32, DB = HD / 64;
   const int b = blockIdx.z, h = blockIdx.y;
   const int start = seq_start[b], n_new = seq_start[b + 1] - start;
@@ -440,12 +446,12 @@ MB_EXPORT int mb_attention_prefill(const void* q, int q_stride, void* out, int o
   dim3 grid((max_new + 63) / 64, nh, B);
   const float scale_log2 = scale * 1.4426950408889634f;
   if (hd == 64)
-    attn_prefill_kernel<64><<<grid, 128, 0, s>>>(
+    mb_launch(attn_prefill_kernel<64>, dim3(grid), dim3(128), 0, s, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kpool, (const bf16*)vpool,
         page_table, max_pages, ring_pages, seq_start, seq_past, seq_slot, nh, nkv, window,
         scale_log2);
   else
-    attn_prefill_kernel<128><<<grid, 128, 0, s>>>(
+    mb_launch(attn_prefill_kernel<128>, dim3(grid), dim3(128), 0, s, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kpool, (const bf16*)vpool,
         page_table, max_pages, ring_pages, seq_start, seq_past, seq_slot, nh, nkv, window,
         scale_log2);

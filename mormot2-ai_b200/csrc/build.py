@@ -28,6 +28,9 @@ NVCC_FLAGS = [
     "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
 
+# more flags for experiments, e.g. MORMOT_B200_NVCC_FLAGS="-DMB_PDL_EARLY"
+NVCC_FLAGS += os.environ.get("MORMOT_B200_NVCC_FLAGS", "").split()
+
 # library name -> source file; headers that every library depends on
 SOURCES = {
     "elementwise": "elementwise.cu",

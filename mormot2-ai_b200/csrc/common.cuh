@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 enum MbDtype { MB_F32 = 0, MB_BF16 = 1 };
 
@@ -30,6 +31,44 @@ static thread_local char g_mb_error[512];
   } while (0)
 
 #define MB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Programmatic dependent launch: a kernel launched through mb_launch may be scheduled while the
+// kernel before it in the stream is still draining; it must call mb_grid_wait() before it
+// touches global memory (the wait returns when the kernels before have completed and their
+// writes are visible). Every kernel that is launched this way waits at its very top, on every
+// path, so that completion stays transitive along a chain of kernels. mb_grid_launch_next()
+// lets the next kernel's CTAs be placed as soon as all CTAs of this one have started.
+__device__ __forceinline__ void mb_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void mb_grid_launch_next() {
+#ifdef MB_PDL_EARLY
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+
+static bool mb_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("MORMOT_B200_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static cudaError_t mb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = mb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 #define MB_DEFINE_LAST_ERROR \
   MB_EXPORT const char* mb_last_error() { return g_mb_error; }

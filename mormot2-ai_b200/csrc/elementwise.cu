@@ -16,6 +16,8 @@ MB_DEFINE_LAST_ERROR
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ x, int H, int V) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= V) id = 0;  // the host refuses such ids before the step
@@ -30,9 +32,9 @@ MB_EXPORT int mb_embed(const void* table, int table_dtype, const int* ids, float
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == MB_F32)
-    embed_kernel<float><<<T, threads, 0, s>>>((const float*)table, ids, x, H, V);
+    mb_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)table, ids, x, H, V);
   else
-    embed_kernel<__nv_bfloat16><<<T, threads, 0, s>>>((const __nv_bfloat16*)table, ids, x, H, V);
+    mb_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s, (const __nv_bfloat16*)table, ids, x, H, V);
   MB_CHECK_LAUNCH("mb_embed");
 }
 
@@ -45,6 +47,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
                                int parts, size_t part_stride, const TW* __restrict__ w,
                                float eps, TO* __restrict__ y, const int* __restrict__ rows,
                                int H) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   __shared__ float red[33];
   extern __shared__ float rowbuf[];  // H floats when parts > 0
   const int r = blockIdx.x;
@@ -79,12 +83,13 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
 
 // The same for rows of 4 * RMS_THREADS * VEC values at most (a multiple of 4): the row is read
 // once with 16-byte loads, kept in registers, and written with 8- or 16-byte stores.
-#define RMS_THREADS 256
-template <typename TW, typename TO, int VEC>
+template <typename TW, typename TO, int VEC, int RMS_THREADS>
 __global__ void __launch_bounds__(RMS_THREADS)
 rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partial, int parts,
                    size_t part_stride, const TW* __restrict__ w, float eps, TO* __restrict__ y,
                    const int* __restrict__ rows, int H) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   __shared__ float red[33];
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -101,8 +106,20 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partial, int
     for (int i = 0; i < VEC; ++i) {
       const int c = (i * RMS_THREADS + threadIdx.x) * 4;
       if (c >= H) continue;
-      for (int p = 0; p < parts; ++p) {
-        const float4 a = *(const float4*)(partial + p * part_stride + (size_t)src * H + c);
+      const float* pp = partial + (size_t)src * H + c;
+      int p = 0;
+      for (; p + 4 <= parts; p += 4) {  // four loads in flight, added in split order
+        const float4 a0 = __ldg((const float4*)(pp + (size_t)p * part_stride));
+        const float4 a1 = __ldg((const float4*)(pp + (size_t)(p + 1) * part_stride));
+        const float4 a2 = __ldg((const float4*)(pp + (size_t)(p + 2) * part_stride));
+        const float4 a3 = __ldg((const float4*)(pp + (size_t)(p + 3) * part_stride));
+        v[i].x = (((v[i].x + a0.x) + a1.x) + a2.x) + a3.x;
+        v[i].y = (((v[i].y + a0.y) + a1.y) + a2.y) + a3.y;
+        v[i].z = (((v[i].z + a0.z) + a1.z) + a2.z) + a3.z;
+        v[i].w = (((v[i].w + a0.w) + a1.w) + a2.w) + a3.w;
+      }
+      for (; p < parts; ++p) {
+        const float4 a = __ldg((const float4*)(pp + (size_t)p * part_stride));
         v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
       }
       *(float4*)(xr + c) = v[i];
@@ -139,16 +156,25 @@ static int rmsnorm_launch(float* x, const float* partial, int parts, size_t part
                           cudaStream_t s) {
   const bool aligned = ((uintptr_t)x & 15) == 0 && ((uintptr_t)partial & 15) == 0 &&
                        (part_stride & 3) == 0 && ((uintptr_t)y & 15) == 0;
-  if (H % 4 == 0 && H <= 4 * RMS_THREADS * 16 && aligned) {
-    const int vec = (H + 4 * RMS_THREADS - 1) / (4 * RMS_THREADS);
-#define RMS_GO(V_)                                                                          \
-  rmsnorm_vec_kernel<TW, TO, V_><<<R, RMS_THREADS, 0, s>>>(x, partial, parts, part_stride,     \
-                                                           (const TW*)w, eps, (TO*)y, rows, H)
-    if (vec <= 1) RMS_GO(1);
-    else if (vec <= 2) RMS_GO(2);
-    else if (vec <= 4) RMS_GO(4);
-    else if (vec <= 8) RMS_GO(8);
-    else RMS_GO(16);
+  if (H % 4 == 0 && H <= 4 * 256 * 16 && aligned) {
+    // few rows (a decode step): 1024 threads a row, so that a thread waits for few loads; many
+    // rows: 256 threads a row and more rows per SM
+#define RMS_GO(V_, T_)                                                                      \
+  mb_launch(rmsnorm_vec_kernel<TW, TO, V_, T_>, dim3(R), dim3(T_), 0, s, x, partial, parts, part_stride,         \
+                                                      (const TW*)w, eps, (TO*)y, rows, H)
+    if (R <= 256 && H > 1024) {
+      const int vec = (H + 4 * 1024 - 1) / (4 * 1024);
+      if (vec <= 1) RMS_GO(1, 1024);
+      else if (vec <= 2) RMS_GO(2, 1024);
+      else RMS_GO(4, 1024);
+    } else {
+      const int vec = (H + 4 * 256 - 1) / (4 * 256);
+      if (vec <= 1) RMS_GO(1, 256);
+      else if (vec <= 2) RMS_GO(2, 256);
+      else if (vec <= 4) RMS_GO(4, 256);
+      else if (vec <= 8) RMS_GO(8, 256);
+      else RMS_GO(16, 256);
+    }
 #undef RMS_GO
     MB_CHECK_LAUNCH("mb_rmsnorm");
   }
@@ -159,7 +185,7 @@ static int rmsnorm_launch(float* x, const float* partial, int parts, size_t part
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) MB_FAIL("mb_rmsnorm: a row of %d values: %s", H, cudaGetErrorString(e));
   }
-  rmsnorm_kernel<TW, TO><<<R, threads, smem, s>>>(x, partial, parts, part_stride,
+  mb_launch(rmsnorm_kernel<TW, TO>, dim3(R), dim3(threads), smem, s, x, partial, parts, part_stride,
                                                   (const TW*)w, eps, (TO*)y, rows, H);
   MB_CHECK_LAUNCH("mb_rmsnorm");
 }
@@ -186,6 +212,8 @@ MB_EXPORT int mb_rmsnorm(float* x, const float* partial, int parts, long long pa
 // in [T, 2I]: gate in columns [0, I), up in [I, 2I); out [T, I] = f32(g / (1 + exp(-g))) * u
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total, int I) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / I;
@@ -205,9 +233,9 @@ MB_EXPORT int mb_swiglu(const void* in, void* out, int dtype, int T, int I, void
                                                                         : 148 * 16);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == MB_F32)
-    swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)in, (float*)out, total, I);
+    mb_launch(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, s, (const float*)in, (float*)out, total, I);
   else
-    swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>((const __nv_bfloat16*)in,
+    mb_launch(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, s, (const __nv_bfloat16*)in,
                                                              (__nv_bfloat16*)out, total, I);
   MB_CHECK_LAUNCH("mb_swiglu");
 }
@@ -225,6 +253,8 @@ __global__ void qk_norm_rope_store_kernel(
     const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
     const int* __restrict__ page_table, int max_pages, int ring_pages, T* __restrict__ kpool,
     T* __restrict__ vpool, int nh, int nkv, int hd, int write_kv) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   extern __shared__ float heads[];  // QK_WARPS x hd
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -289,6 +319,8 @@ qk_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partia
                const int* __restrict__ page_table, int max_pages, int ring_pages,
                __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int nh,
                int nkv, int write_kv) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   constexpr int HD = 64 * V, HALF = 32 * V;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -302,12 +334,14 @@ qk_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partia
   if (PARTIAL) {
 #pragma unroll
     for (int j = 0; j < V; ++j) a[j] = b[j] = 0.f;
+    const float* src0 = partial + (size_t)t * total * HD + col;
+#pragma unroll 4
     for (int p = 0; p < parts; ++p) {
-      const float* src = partial + p * part_stride + (size_t)t * total * HD + col;
+      const float* src = src0 + (size_t)p * part_stride;
 #pragma unroll
       for (int j = 0; j < V; ++j) {
-        a[j] += src[j];
-        b[j] += src[HALF + j];
+        a[j] += __ldg(src + j);
+        b[j] += __ldg(src + HALF + j);
       }
     }
   } else {
@@ -382,7 +416,7 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
   if (fast) {
     typedef __nv_bfloat16 bf;
 #define QKF(V_, TW_, P_)                                                                       \
-  qk_fast_kernel<V_, TW_, P_><<<grid, QK_WARPS * 32, 0, s>>>(                                   \
+  mb_launch(qk_fast_kernel<V_, TW_, P_>, dim3(grid), dim3(QK_WARPS * 32), 0, s,                                    \
       (bf*)qkv, partial, parts, (size_t)part_stride, (bf*)q_out, (const TW_*)q_norm,           \
       (const TW_*)k_norm, eps, inv_freq, tok_seq, tok_pos, seq_slot, page_table, max_pages,    \
       ring_pages, (bf*)kpool, (bf*)vpool, nh, nkv, write_kv)
@@ -396,7 +430,7 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
   }
   const size_t smem = (size_t)QK_WARPS * hd * sizeof(float);
 #define QK_LAUNCH(T_, TW_)                                                                     \
-  qk_norm_rope_store_kernel<T_, TW_><<<grid, QK_WARPS * 32, smem, s>>>(                        \
+  mb_launch(qk_norm_rope_store_kernel<T_, TW_>, dim3(grid), dim3(QK_WARPS * 32), smem, s,                         \
       (T_*)qkv, (const TW_*)q_norm, (const TW_*)k_norm, eps, inv_freq, rot_dim, tok_seq,       \
       tok_pos, seq_slot, page_table, max_pages, ring_pages, (T_*)kpool, (T_*)vpool, nh, nkv,   \
       hd, write_kv)
@@ -414,6 +448,8 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
 __global__ void advance_decode_kernel(int* __restrict__ tok_ids, int* __restrict__ tok_pos,
                                       const int* __restrict__ chosen, int* __restrict__ history,
                                       int B) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   const int t = chosen[b];
@@ -425,7 +461,7 @@ __global__ void advance_decode_kernel(int* __restrict__ tok_ids, int* __restrict
 MB_EXPORT int mb_advance_decode(int* tok_ids, int* tok_pos, const int* chosen, int* history,
                                 int B, void* stream) {
   if (B <= 0) return 0;
-  advance_decode_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream>>>(tok_ids, tok_pos,
+  mb_launch(advance_decode_kernel, dim3((B + 127) / 128), dim3(128), 0, (cudaStream_t)stream, tok_ids, tok_pos,
                                                                           chosen, history, B);
   MB_CHECK_LAUNCH("mb_advance_decode");
 }

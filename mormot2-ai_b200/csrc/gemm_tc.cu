@@ -106,6 +106,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *slot_ptr;
+  // everything above touched only this CTA's shared and tensor memory; from here on the
+  // kernels before in the stream must have finished
+  mb_grid_wait();
+  mb_grid_launch_next();
 
   if (warp == 0) {
     if (elect_one()) {
@@ -231,6 +235,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits,
                                      long long stride, void* __restrict__ C, int c_dtype,
                                      long long ldc, int M, int N, int mode) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   const size_t total = (size_t)M * N;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -259,7 +265,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, in
     configured = true;
   }
   dim3 grid((rowsA + p.tile_rows - 1) / p.tile_rows, (rowsB + BN - 1) / BN, p.splits);
-  gemm_tc_kernel<BN, SWAP><<<grid, TC_THREADS, p.smem, s>>>(
+  mb_launch(gemm_tc_kernel<BN, SWAP>, dim3(grid), dim3(TC_THREADS), p.smem, s, 
       tmA, tmB, C, c_dtype, ldc, rowsA, rowsB, K, p.kb_per_split, mode, partial, pstride, pld,
       p.tile_rows, p.stages, p.a_stage, error);
   MB_CHECK_LAUNCH("mb_gemm_tc");
@@ -380,7 +386,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
   if (p.splits > 1 && !defer) {
     const size_t total = (size_t)M * N;
     const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
-    splitk_reduce_kernel<<<blocks, 256, 0, s>>>(workspace, p.splits, pstride, C, c_dtype, ldc, M,
+    mb_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, s, workspace, p.splits, pstride, C, c_dtype, ldc, M,
                                                 N, epilogue);
     MB_CHECK_LAUNCH("mb_gemm_tc reduce");
   }

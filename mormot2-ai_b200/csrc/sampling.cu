@@ -67,6 +67,8 @@ __device__ Best block_argmax(const float* __restrict__ row, int V, Best* sh) {
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, size_t stride, int V, int* __restrict__ out) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   __shared__ Best sh[32];
   const Best b = block_argmax(logits + blockIdx.x * stride, V, sh);
   if (threadIdx.x == 0) out[blockIdx.x] = b.i;
@@ -79,6 +81,8 @@ argmax_kernel(const float* __restrict__ logits, size_t stride, int V, int* __res
 __global__ void __launch_bounds__(256)
 argmax_chunks_kernel(const float* __restrict__ logits, size_t stride, int V,
                      Best* __restrict__ partial, int chunks) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   __shared__ Best sh[32];
   const int i0 = blockIdx.x * ARGMAX_CHUNK;
   const int n = min(ARGMAX_CHUNK, V - i0);
@@ -92,6 +96,8 @@ argmax_chunks_kernel(const float* __restrict__ logits, size_t stride, int V,
 
 __global__ void __launch_bounds__(128)
 argmax_final_kernel(const Best* __restrict__ partial, int chunks, int* __restrict__ out) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   __shared__ Best sh[4];
   Best b = {0.f, -1};
   for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
@@ -127,11 +133,11 @@ MB_EXPORT int mb_argmax(const float* logits, long long stride, int rows, int V, 
   cudaStream_t s = (cudaStream_t)stream;
   const int chunks = (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
   if (scratch && chunks > 4 && rows <= 65535 && scratch_bytes >= mb_argmax_scratch(rows, V)) {
-    argmax_chunks_kernel<<<dim3(chunks, rows), 256, 0, s>>>(logits, (size_t)stride, V,
+    mb_launch(argmax_chunks_kernel, dim3(dim3(chunks, rows)), dim3(256), 0, s, logits, (size_t)stride, V,
                                                            (Best*)scratch, chunks);
-    argmax_final_kernel<<<rows, 128, 0, s>>>((const Best*)scratch, chunks, out);
+    mb_launch(argmax_final_kernel, dim3(rows), dim3(128), 0, s, (const Best*)scratch, chunks, out);
   } else {
-    argmax_kernel<<<rows, SAMPLE_THREADS, 0, s>>>(logits, (size_t)stride, V, out);
+    mb_launch(argmax_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, s, logits, (size_t)stride, V, out);
   }
   MB_CHECK_LAUNCH("mb_argmax");
 }
@@ -146,6 +152,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, size_t stride, int V, double inv_t,
               const int* __restrict__ state_index, unsigned long long* __restrict__ states,
               int* __restrict__ out) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   __shared__ Best sh[32];
   __shared__ double sums[SAMPLE_THREADS];
   __shared__ double target_sh;
@@ -208,7 +216,7 @@ MB_EXPORT int mb_sample(const float* logits, long long stride, int rows, int V,
   if (rows <= 0) return 0;
   if (V <= 0) MB_FAIL("mb_sample: a vocabulary of %d", V);
   if (!(temperature >= 1e-30)) MB_FAIL("mb_sample: a temperature of %g is greedy", temperature);
-  sample_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
+  mb_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, 
       logits, (size_t)stride, V, 1.0 / temperature, state_index, states, out);
   MB_CHECK_LAUNCH("mb_sample");
 }
@@ -253,6 +261,8 @@ sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, d
                        const int* __restrict__ state_index, unsigned long long* __restrict__ states,
                        unsigned long long* __restrict__ scratch, size_t scratch_stride,
                        int* __restrict__ out) {
+  mb_grid_wait();
+  mb_grid_launch_next();
   __shared__ Best sh[32];
   __shared__ double dsh[33];
   __shared__ int count_sh;
@@ -381,7 +391,7 @@ MB_EXPORT int mb_sample_filtered(const float* logits, long long stride, int rows
     MB_FAIL("mb_sample_filtered: top_k %d, top_p %g, min_p %g", top_k, top_p, min_p);
   if (scratch_stride < V || (scratch_stride & (scratch_stride - 1)))
     MB_FAIL("mb_sample_filtered: a scratch row of %lld words for %d tokens", scratch_stride, V);
-  sample_filtered_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
+  mb_launch(sample_filtered_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, 
       logits, (size_t)stride, V, 1.0 / temperature, top_k, top_p, min_p, state_index, states,
       scratch, (size_t)scratch_stride, out);
   MB_CHECK_LAUNCH("mb_sample_filtered");

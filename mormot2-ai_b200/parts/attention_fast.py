@@ -20,9 +20,13 @@ def decode_split(line, T: int, nh: int, nkv: int, sms: int, window: int) -> Tupl
     if window > 0:
         pages = min(pages, pages_for(window) + 1)
     subs = (nh // nkv + 15) // 16
-    per_split = max(1, T * nkv * subs)
-    splits = max(1, min(pages, -(-4 * sms // per_split)))
-    pages_per_split = -(-pages // splits)
+    groups = max(1, T * nkv * subs)
+    # a CTA has four warps that take pages in turn: one page a warp (then 2, 4, ...) until the
+    # grid is no more than eight CTAs for every SM
+    per_warp = 1
+    while groups * -(-pages // (4 * per_warp)) > 8 * sms and 4 * per_warp < pages:
+        per_warp *= 2
+    pages_per_split = min(pages, 4 * per_warp)
     return -(-pages // pages_per_split), pages_per_split
 
 
