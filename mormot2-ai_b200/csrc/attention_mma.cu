@@ -15,6 +15,7 @@
 // fragments use a permutation of the dimensions under which every thread's values lie
 // contiguous in memory.
 #include "mma_common.cuh"
+#include "tc_common.cuh"
 
 MB_DEFINE_LAST_ERROR
 
@@ -82,20 +83,49 @@ __device__ __forceinline__ void load_q(const bf16* q0, const bf16* q1, int c, ui
   }
 }
 
+// 16 bytes of a tile in shared memory
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+
+// `bytes` contiguous bytes from global to shared memory (both 16-byte aligned), completing `bar`
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+#define DEC_STAGES 3
+
+// One CTA per (token, KV head [x 16 query heads of its group], split). Warp 4 streams the
+// pages of this split (every `splits`-th page of the sequence) into shared memory, a whole K
+// tile and a whole V tile per page (16 KB each for heads of 128) by bulk asynchronous copies,
+// three pages ahead. Warps 0-3 take 16 keys of every page each.
 template <int HD>
-__global__ void __launch_bounds__(DEC_WARPS * 32, 2)
+__global__ void __launch_bounds__((DEC_WARPS + 1) * 32, 2)
 attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kpool,
                    const bf16* __restrict__ vpool, const int* __restrict__ page_table,
                    int max_pages, int ring_pages, const int* __restrict__ tok_seq,
                    const int* __restrict__ tok_pos, const int* __restrict__ seq_slot, int nh,
-                   int nkv, int window, float scale_log2, int pages_per_split,
-                   float* __restrict__ part_o, float* __restrict__ part_ml) {
+                   int nkv, int window, float scale_log2, float* __restrict__ part_o,
+                   float* __restrict__ part_ml, int* __restrict__ error) {
   mb_grid_wait();
   mb_grid_launch_next();
   constexpr int CH = HD / 32;  // 32-dim chunks of q·k
   constexpr int DB = HD / 64;  // 64-dim blocks of p·v
-  __shared__ float sm_m[DEC_WARPS][16], sm_l[DEC_WARPS][16];
-  __shared__ float sm_o[DEC_WARPS][16][HD];
+  constexpr uint32_t TILE = MB_PAGE * HD * 2;  // bytes of a page's keys (or values)
+  extern __shared__ __align__(128) uint8_t dec_smem[];
+  // [stages][K tile | V tile], then the barriers; after the loop the tiles' memory holds the
+  // warps' partial results for the merge
+  const uint32_t tiles = smem_u32(dec_smem);
+  const uint32_t bars = tiles + DEC_STAGES * 2 * TILE;
+  const uint32_t full0 = bars, empty0 = bars + 8 * DEC_STAGES;
 
   const int s = blockIdx.x, S = gridDim.x, t = blockIdx.z;
   const int G = nh / nkv, subs = (G + 15) / 16;
@@ -108,17 +138,18 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   const int pos = tok_pos[t];
   const int slot = seq_slot[tok_seq[t]];
   const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
-  const int p_first = lo / MB_PAGE, p_last = pos / MB_PAGE;
-  const int my_first = p_first + s * pages_per_split;
-  const int my_last = min(p_last, my_first + pages_per_split - 1);
+  const int p_first = lo / MB_PAGE + s, p_last = pos / MB_PAGE;
+  const int n_pages = p_first <= p_last ? (p_last - p_first) / S + 1 : 0;  // p_first + i * S
 
-  // q fragments of rows r and r + 8: 8 consecutive dims per 32-dim chunk
-  uint4 qa[CH], qb[CH];
-  {
-    const bf16* qrow = q + (size_t)t * q_stride + (size_t)(h0 + r) * HD;
-    load_q<HD>(r < rows_valid ? qrow : nullptr, r + 8 < rows_valid ? qrow + 8 * HD : nullptr, c,
-               qa, qb);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < DEC_STAGES; ++i) {
+      mbar_init(full0 + 8 * i, 1);
+      mbar_init(empty0 + 8 * i, DEC_WARPS);
+    }
+    mbar_fence_init();
   }
+  __syncthreads();
+
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   float o[DB][8][4];
 #pragma unroll
@@ -128,95 +159,157 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
 #pragma unroll
       for (int e = 0; e < 4; ++e) o[db][j][e] = 0.f;
 
-  for (int p = my_first + warp; p <= my_last; p += DEC_WARPS) {
-    const int lp = ring_pages > 0 ? p % ring_pages : p;
-    const int page = page_table[(size_t)slot * max_pages + lp];
-    const bf16* kbase = kpool + ((size_t)page * nkv + g) * MB_PAGE * HD;
-    const bf16* vbase = vpool + ((size_t)page * nkv + g) * MB_PAGE * HD;
-    const int key0 = p * MB_PAGE;
-
-    float sc[8][4];
-    qk_page<HD>(qa, qb, kbase, r, c, sc);
-    // mask (the same for every row: one token), scale into the log2 domain, row maxima
-    float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int key = key0 + u * 8 + 2 * c + e;
-        const bool ok = key >= lo && key <= pos;
-        sc[u][e] = ok ? sc[u][e] * scale_log2 : -INFINITY;
-        sc[u][2 + e] = ok ? sc[u][2 + e] * scale_log2 : -INFINITY;
-        mx0 = fmaxf(mx0, sc[u][e]);
-        mx1 = fmaxf(mx1, sc[u][2 + e]);
+  if (warp == DEC_WARPS) {
+    // producer: the lanes fetch the ids of up to 32 pages at once, lane 0 issues the copies
+    int st = 0;
+    uint32_t ph = 0;
+    for (int i0 = 0; i0 < n_pages; i0 += 32) {
+      int mine = 0;
+      if (i0 + lane < n_pages) {
+        const int p = p_first + (i0 + lane) * S;
+        mine = page_table[(size_t)slot * max_pages + (ring_pages > 0 ? p % ring_pages : p)];
+      }
+      const int n = min(32, n_pages - i0);
+      for (int i = 0; i < n; ++i) {
+        const int page = __shfl_sync(0xffffffffu, mine, i);
+        if (lane == 0) {
+          mbar_wait(empty0 + 8 * st, ph ^ 1, error, 4);
+          mbar_expect_tx(full0 + 8 * st, 2 * TILE);
+          const size_t at = ((size_t)page * nkv + g) * MB_PAGE * HD;
+          bulk_copy(tiles + st * 2 * TILE, kpool + at, TILE, full0 + 8 * st);
+          bulk_copy(tiles + st * 2 * TILE + TILE, vpool + at, TILE, full0 + 8 * st);
+        }
+        if (++st == DEC_STAGES) { st = 0; ph ^= 1; }
       }
     }
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-    // a page of this split always holds at least one key of [lo, pos], so n0, n1 are finite
-    const float c0 = exp2f(m0 - n0), c1 = exp2f(m1 - n1);
-    m0 = n0;
-    m1 = n1;
-    float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        sc[u][e] = exp2f(sc[u][e] - n0);
-        sc[u][2 + e] = exp2f(sc[u][2 + e] - n1);
-        s0 += sc[u][e];
-        s1 += sc[u][2 + e];
-      }
+  } else {
+    uint4 qa[CH], qb[CH];
+    {
+      const bf16* qrow = q + (size_t)t * q_stride + (size_t)(h0 + r) * HD;
+      load_q<HD>(r < rows_valid ? qrow : nullptr, r + 8 < rows_valid ? qrow + 8 * HD : nullptr, c,
+                 qa, qb);
     }
-    l0 = l0 * c0 + s0;
-    l1 = l1 * c1 + s1;
+    int st = 0;
+    uint32_t ph = 0;
+    for (int i = 0; i < n_pages; ++i) {
+      const int key0 = (p_first + i * S) * MB_PAGE + 16 * warp;  // this warp's 16 keys
+      mbar_wait(full0 + 8 * st, ph, error, 5);
+      const uint32_t ks = tiles + st * 2 * TILE + (uint32_t)(16 * warp) * HD * 2;
+      const uint32_t vs = ks + TILE;
+      float sc[2][4];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        sc[u][0] = sc[u][1] = sc[u][2] = sc[u][3] = 0.f;
+        const uint32_t krow = ks + (uint32_t)(u * 8 + r) * HD * 2 + c * 16;
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch) {
+          const uint4 kb = lds16(krow + ch * 64);
+          mma_bf16(sc[u], qa[ch].x, qb[ch].x, qa[ch].y, qb[ch].y, kb.x, kb.y);
+          mma_bf16(sc[u], qa[ch].z, qb[ch].z, qa[ch].w, qb[ch].w, kb.z, kb.w);
+        }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = key0 + u * 8 + 2 * c + e;
+          const bool ok = key >= lo && key <= pos;
+          sc[u][e] = ok ? sc[u][e] * scale_log2 : -INFINITY;
+          sc[u][2 + e] = ok ? sc[u][2 + e] * scale_log2 : -INFINITY;
+          mx0 = fmaxf(mx0, sc[u][e]);
+          mx1 = fmaxf(mx1, sc[u][2 + e]);
+        }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+      // this warp's 16 keys of the page may all lie outside [lo, pos]: keep exp2 off inf - inf
+      const float base0 = n0 == -INFINITY ? 0.f : n0, base1 = n1 == -INFINITY ? 0.f : n1;
+      const float c0 = exp2f(m0 - base0), c1 = exp2f(m1 - base1);
+      m0 = n0;
+      m1 = n1;
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          sc[u][e] = exp2f(sc[u][e] - base0);
+          sc[u][2 + e] = exp2f(sc[u][2 + e] - base1);
+          s0 += sc[u][e];
+          s1 += sc[u][2 + e];
+        }
+      l0 = l0 * c0 + s0;
+      l1 = l1 * c1 + s1;
+      const uint32_t a0 = pack_bf16(sc[0][0], sc[0][1]), a1 = pack_bf16(sc[0][2], sc[0][3]);
+      const uint32_t a2 = pack_bf16(sc[1][0], sc[1][1]), a3 = pack_bf16(sc[1][2], sc[1][3]);
+      const uint32_t vrow = vs + (uint32_t)(2 * c) * HD * 2 + r * 16;
+#pragma unroll
+      for (int db = 0; db < DB; ++db) {
+        const uint4 va = lds16(vrow + db * 128);
+        const uint4 vb = lds16(vrow + HD * 2 + db * 128);
+        const uint4 vc = lds16(vrow + 8 * HD * 2 + db * 128);
+        const uint4 vd = lds16(vrow + 9 * HD * 2 + db * 128);
+        const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+        const uint32_t wc[4] = {vc.x, vc.y, vc.z, vc.w}, wd[4] = {vd.x, vd.y, vd.z, vd.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[db][j][0] *= c0;
+          o[db][j][1] *= c0;
+          o[db][j][2] *= c1;
+          o[db][j][3] *= c1;
+          const int w = j >> 1;
+          const uint32_t b0 = (j & 1) ? pack_hi(wa[w], wb[w]) : pack_lo(wa[w], wb[w]);
+          const uint32_t b1 = (j & 1) ? pack_hi(wc[w], wd[w]) : pack_lo(wc[w], wd[w]);
+          mma_bf16(o[db][j], a0, a1, a2, a3, b0, b1);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * st);  // this warp is done with the stage
+      if (++st == DEC_STAGES) { st = 0; ph ^= 1; }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  }
+  // every copy has landed and been read: the tiles' memory now holds the warps' results
+  __syncthreads();
+  float* sm_o = (float*)dec_smem;                       // [DEC_WARPS][16][HD]
+  float* sm_m = sm_o + DEC_WARPS * 16 * HD;             // [DEC_WARPS][16]
+  float* sm_l = sm_m + DEC_WARPS * 16;                  // [DEC_WARPS][16]
+  if (warp < DEC_WARPS) {
+    if (c == 0) {
+      sm_m[warp * 16 + r] = m0;
+      sm_m[warp * 16 + r + 8] = m1;
+      sm_l[warp * 16 + r] = l0;
+      sm_l[warp * 16 + r + 8] = l1;
+    }
 #pragma unroll
     for (int db = 0; db < DB; ++db)
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        o[db][j][0] *= c0;
-        o[db][j][1] *= c0;
-        o[db][j][2] *= c1;
-        o[db][j][3] *= c1;
+        const int d0 = db * 64 + (2 * c) * 8 + j, d1 = d0 + 8;
+        sm_o[(warp * 16 + r) * HD + d0] = o[db][j][0];
+        sm_o[(warp * 16 + r) * HD + d1] = o[db][j][1];
+        sm_o[(warp * 16 + r + 8) * HD + d0] = o[db][j][2];
+        sm_o[(warp * 16 + r + 8) * HD + d1] = o[db][j][3];
       }
-    pv_page<HD>(sc, vbase, r, c, o);
   }
-  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  if (c == 0) {
-    sm_m[warp][r] = m0;
-    sm_m[warp][r + 8] = m1;
-    sm_l[warp][r] = l0;
-    sm_l[warp][r + 8] = l1;
-  }
-#pragma unroll
-  for (int db = 0; db < DB; ++db)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int d0 = db * 64 + (2 * c) * 8 + j, d1 = d0 + 8;
-      sm_o[warp][r][d0] = o[db][j][0];
-      sm_o[warp][r][d1] = o[db][j][1];
-      sm_o[warp][r + 8][d0] = o[db][j][2];
-      sm_o[warp][r + 8][d1] = o[db][j][3];
-    }
   __syncthreads();
   for (int idx = threadIdx.x; idx < rows_valid * HD; idx += blockDim.x) {
     const int row = idx / HD, d = idx - row * HD;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm_m[w][row]);
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm_m[w * 16 + row]);
     float L = 0.f, acc = 0.f;
     if (M > -INFINITY) {
 #pragma unroll
       for (int w = 0; w < DEC_WARPS; ++w) {
-        const float f = exp2f(sm_m[w][row] - M);  // 0 for a warp without pages
-        L += sm_l[w][row] * f;
-        acc += sm_o[w][row][d] * f;
+        const float f = exp2f(sm_m[w * 16 + row] - M);  // 0 for a warp without keys
+        L += sm_l[w * 16 + row] * f;
+        acc += sm_o[(w * 16 + row) * HD + d] * f;
       }
     }
     const size_t at = ((size_t)t * nh + h0 + row) * S + s;
@@ -256,22 +349,24 @@ MB_EXPORT long long mb_attention_decode_scratch(int T, int nh, int hd, int split
 }
 
 // out[t, h, :] for every token t (each with its own sequence and position: a decode step, or
-// any few tokens). `splits` CTAs share a sequence's pages, `pages_per_split` each; both are
-// chosen by the caller from the cache's capacity (splits * pages_per_split >= the most pages
-// that a sequence can hold in this line). `scratch`: float32, at least
-// mb_attention_decode_scratch(...) values; its contents are not kept between calls.
+// any few tokens). `splits` CTAs share a sequence's pages (CTA s takes the pages s, s + splits,
+// ...); the caller chooses it from the batch and the SM count, not from the lengths of the
+// moment, so that a captured launch stays valid. `scratch`: float32, at least
+// mb_attention_decode_scratch(...) values; its contents are not kept between calls. `error`:
+// a device word that receives 4 or 5 if a wait of the kernel's copy pipeline ran out.
 MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int out_stride,
                                   const void* kpool, const void* vpool, const int* page_table,
                                   int max_pages, int ring_pages, const int* tok_seq,
                                   const int* tok_pos, const int* seq_slot, int T, int nh, int nkv,
-                                  int hd, int window, float scale, int splits,
-                                  int pages_per_split, float* scratch, long long scratch_floats,
-                                  void* stream) {
+                                  int hd, int window, float scale, int splits, float* scratch,
+                                  long long scratch_floats, int* error, void* stream) {
   if (T <= 0) return 0;
   if (hd != 64 && hd != 128)
     MB_FAIL("mb_attention_decode: heads of %d values are not supported (64 or 128)", hd);
   if (nkv <= 0 || nh % nkv) MB_FAIL("mb_attention_decode: %d heads on %d KV heads", nh, nkv);
-  if (splits <= 0 || pages_per_split <= 0) MB_FAIL("mb_attention_decode: %d splits", splits);
+  if (splits <= 0 || splits > 65535) MB_FAIL("mb_attention_decode: %d splits", splits);
+  if (((uintptr_t)kpool & 15) || ((uintptr_t)vpool & 15))
+    MB_FAIL("mb_attention_decode: the cache pools are not 16-byte aligned");
   if (((uintptr_t)q & 15) || (q_stride & 7))
     MB_FAIL("mb_attention_decode: q is not 16-byte aligned (stride %d)", q_stride);
   const long long need = mb_attention_decode_scratch(T, nh, hd, splits);
@@ -285,12 +380,23 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(splits, nkv * subs, T), mgrid(T, nh);
 #define GO(HD_)                                                                                \
-  mb_launch(attn_decode_kernel<HD_>, dim3(grid), dim3(DEC_WARPS * 32), 0, s,                                       \
-      (const bf16*)q, q_stride, (const bf16*)kpool, (const bf16*)vpool, page_table, max_pages, \
-      ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, window, scale_log2, pages_per_split,    \
-      part_o, part_ml);                                                                        \
-  mb_launch(attn_merge_kernel<HD_>, dim3(mgrid), dim3(HD_), 0, s, part_o, part_ml, splits, (bf16*)out, out_stride, nh)
-  if (hd == 64) { GO(64); } else { GO(128); }
+  {                                                                                            \
+    constexpr int smem = DEC_STAGES * 2 * MB_PAGE * HD_ * 2 + 64;                              \
+    static bool configured = false;                                                            \
+    if (!configured) {                                                                         \
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD_>,                            \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+      if (e != cudaSuccess) MB_FAIL("mb_attention_decode: %s", cudaGetErrorString(e));         \
+      configured = true;                                                                       \
+    }                                                                                          \
+    mb_launch(attn_decode_kernel<HD_>, grid, dim3((DEC_WARPS + 1) * 32), smem, s,              \
+              (const bf16*)q, q_stride, (const bf16*)kpool, (const bf16*)vpool, page_table,    \
+              max_pages, ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, window, scale_log2,  \
+              part_o, part_ml, error);                                                         \
+    mb_launch(attn_merge_kernel<HD_>, mgrid, dim3(HD_), 0, s, (const float*)part_o,            \
+              (const float*)part_ml, splits, (bf16*)out, out_stride, nh);                      \
+  }
+  if (hd == 64) GO(64) else GO(128)
 #undef GO
   MB_CHECK_LAUNCH("mb_attention_decode");
 }
@@ -474,8 +580,8 @@ MB_EXPORT int mb_attention_decode_static(const void* q, int q_stride, void* out,
                                          const int* page_table, int max_pages, int ring_pages,
                                          const int* tok_seq, const int* tok_pos,
                                          const int* seq_slot, int T, int nh, int nkv, int hd,
-                                         int window, float scale, int splits,
-                                         int pages_per_split, void* stream) {
+                                         int window, float scale, int splits, int* error,
+                                         void* stream) {
   if (T <= 0) return 0;
   if (nh <= 0 || hd <= 0 || splits <= 0)
     MB_FAIL("mb_attention_decode_static: %d heads of %d, %d splits", nh, hd, splits);
@@ -500,6 +606,6 @@ MB_EXPORT int mb_attention_decode_static(const void* q, int q_stride, void* out,
   }
   return mb_attention_decode(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
                              ring_pages, tok_seq, tok_pos, seq_slot, T, nh, nkv, hd, window,
-                             scale, splits, pages_per_split, g_static_scratch_ptr[device],
-                             MB_ATTENTION_DECODE_STATIC_FLOATS, stream);
+                             scale, splits, g_static_scratch_ptr[device],
+                             MB_ATTENTION_DECODE_STATIC_FLOATS, error, stream);
 }

@@ -44,12 +44,15 @@ extern "C" {
  * threads) write the same memory and race: keep the calls of one device in one stream, or
  * order them yourself.
  *
+ * `error`, as for mb_attention_decode, is a device word of the caller's (it may be null) that
+ * receives a code if a bounded wait inside the kernel runs out.
+ *
  * Returns 0 after the launch, -1 on refusal. */
 int mb_attention_decode_static(const void* q, int q_stride, void* out, int out_stride,
                                const void* kpool, const void* vpool, const int* page_table,
                                int max_pages, int ring_pages, const int* tok_seq,
                                const int* tok_pos, const int* seq_slot, int T, int nh, int nkv,
-                               int hd, int window, float scale, int splits, int pages_per_split,
+                               int hd, int window, float scale, int splits, int* error,
                                void* stream);
 
 #ifdef __cplusplus

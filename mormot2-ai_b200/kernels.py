@@ -265,21 +265,21 @@ def sample_filtered(logits: torch.Tensor, sampling, state_index: torch.Tensor,
 
 
 def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv, hd,
-                     window: int, scale: float, splits: int, pages_per_split: int,
-                     scratch: torch.Tensor) -> None:
+                     window: int, scale: float, splits: int, scratch: torch.Tensor,
+                     error: Optional[torch.Tensor] = None) -> None:
     """Attention of single tokens (a decode step) over the paged cache on the tensor cores; the
-    pages of a sequence are shared out over ``splits`` CTAs."""
+    pages of a sequence are dealt out over ``splits`` CTAs."""
     T = out.shape[0]
     _contig(out, "out")
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert scratch.dtype == torch.float32 and scratch.is_contiguous()
     _call("attention_mma", "mb_attention_decode",
           [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
-           _i, _vp, _ll, _vp],
+           _vp, _ll, _vp, _vp],
           _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.tok_seq),
           _ptr(step.tok_pos), _ptr(step.seq_slot), T, nh, nkv, hd, window, float(scale),
-          splits, pages_per_split, _ptr(scratch), scratch.numel(), _stream(), launches=2)
+          splits, _ptr(scratch), scratch.numel(), _ptr(error), _stream(), launches=2)
 
 
 def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv,

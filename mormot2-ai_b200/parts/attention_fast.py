@@ -12,22 +12,18 @@ from ..cache.pages import pages_for
 FAST_HEAD_DIMS = (64, 128)
 
 
-def decode_split(line, T: int, nh: int, nkv: int, sms: int, window: int) -> Tuple[int, int]:
-    """(splits, pages per split) for a decode step of T tokens: enough CTAs to fill the GPU a
-    few times over, sized by the most pages that a sequence can hold in this line (not by the
-    lengths of the moment: a captured launch must stay valid as sequences grow)."""
+def decode_splits(line, T: int, nh: int, nkv: int, sms: int, window: int) -> int:
+    """Over how many CTAs the pages of a sequence are dealt out in a decode step of T tokens.
+    Every CTA pays a fixed price (index loads before its first key, the merge at its end), so
+    few, long CTAs win: as many as give one round of two CTAs per SM, and no more than the most
+    pages that a sequence can hold in this line (the lengths of the moment do not count: a
+    captured launch must stay valid as sequences grow)."""
     pages = line.max_pages
     if window > 0:
         pages = min(pages, pages_for(window) + 1)
     subs = (nh // nkv + 15) // 16
     groups = max(1, T * nkv * subs)
-    # a CTA has four warps that take pages in turn: one page a warp (then 2, 4, ...) until the
-    # grid is no more than eight CTAs for every SM
-    per_warp = 1
-    while groups * -(-pages // (4 * per_warp)) > 8 * sms and 4 * per_warp < pages:
-        per_warp *= 2
-    pages_per_split = min(pages, 4 * per_warp)
-    return -(-pages // pages_per_split), pages_per_split
+    return max(1, min((2 * sms) // groups, pages))
 
 
 def run(rt, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> bool:
@@ -35,12 +31,12 @@ def run(rt, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> bool:
     if hd not in FAST_HEAD_DIMS or q.dtype != torch.bfloat16 or q_stride % 8 or q.data_ptr() % 16:
         return False
     if step.decode:
-        splits, pps = decode_split(line, step.T, nh, nkv, rt.sms, window)
+        splits = decode_splits(line, step.T, nh, nkv, rt.sms, window)
         need = step.T * nh * splits * (hd + 2)
         if rt.workspace is None or rt.workspace.numel() < need:
             return False
-        K.attention_decode(q, q_stride, out, step, line, nh, nkv, hd, window, scale, splits, pps,
-                           rt.workspace)
+        K.attention_decode(q, q_stride, out, step, line, nh, nkv, hd, window, scale, splits,
+                           rt.workspace, rt.error_word)
         return True
     if out.stride(0) % 8 or out.data_ptr() % 16:
         return False

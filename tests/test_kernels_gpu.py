@@ -173,12 +173,12 @@ def run_attention(kind, q, out, step, line, nh, nkv, hd, window, scale, splits=N
     if kind == "prefill":
         K.attention_prefill(q, nh * hd, out, step, line, nh, nkv, hd, window, scale)
         return
-    pages = line.max_pages
     splits = splits or 3
-    pps = -(-pages // splits)
     scratch = torch.empty(out.shape[0] * nh * splits * (hd + 2) + 5, device=DEV)
-    K.attention_decode(q, nh * hd, out, step, line, nh, nkv, hd, window, scale,
-                       -(-pages // pps), pps, scratch)
+    error = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.attention_decode(q, nh * hd, out, step, line, nh, nkv, hd, window, scale, splits, scratch,
+                       error)
+    assert int(error.item()) == 0
 
 
 ATTENTION_CASES = [("simt", 4, 2, 16, "float32"), ("simt", 6, 1, 48, "float32"),
@@ -215,7 +215,7 @@ def test_attention_over_the_paged_cache(kind, nh, nkv, hd, dtype):
         q = torch.tensor(rng.standard_normal((T, nh * hd)), dtype=torch.float32).to(dt)
         out = torch.empty(T, nh * hd, dtype=dt, device=DEV)
         scale = 1.0 / math.sqrt(hd)
-        for splits in ((1, 3, 4) if kind == "decode" else (None,)):
+        for splits in ((1, 3, 4, 7) if kind == "decode" else (None,)):
             out.zero_()
             run_attention(kind, q.to(DEV), out, step, line, nh, nkv, hd, window, scale, splits)
             got = out.float().cpu().numpy().reshape(T, nh, hd)

@@ -18,7 +18,7 @@ pytestmark = pytest.mark.gpu
 
 _vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 ARGTYPES = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
-            _i, _vp]
+            _vp, _vp]
 LIMIT = 4 * 1024 * 1024          # MB_ATTENTION_DECODE_STATIC_FLOATS
 
 
@@ -29,11 +29,11 @@ def static_entry():
     return lib, fn
 
 
-def call_static(fn, q, out, step, line, nh, nkv, hd, window, scale, splits, pps):
+def call_static(fn, q, out, step, line, nh, nkv, hd, window, scale, splits):
     return fn(q.data_ptr(), nh * hd, out.data_ptr(), out.stride(0), line.k.data_ptr(),
               line.v.data_ptr(), line.page_table.data_ptr(), line.max_pages, line.ring_pages,
               step.tok_seq.data_ptr(), step.tok_pos.data_ptr(), step.seq_slot.data_ptr(),
-              out.shape[0], nh, nkv, hd, window, scale, splits, pps,
+              out.shape[0], nh, nkv, hd, window, scale, splits, None,
               torch.cuda.current_stream().cuda_stream)
 
 
@@ -56,15 +56,13 @@ def test_two_calls_in_a_row_equal_the_existing_entry_point():
     before = torch.cuda.memory_allocated()
     for seed, lens, window, splits in ((1, [600, 3, 129], 0, 4), (2, [64, 500], 90, 10)):
         line, step, q = case(seed, lens, nh, nkv, hd, window)
-        pps = -(-line.max_pages // splits)
-        used = -(-line.max_pages // pps)
         want = torch.empty(len(lens), nh * hd, dtype=torch.bfloat16, device=DEV)
-        scratch = torch.empty(len(lens) * nh * used * (hd + 2), device=DEV)
-        K.attention_decode(q, nh * hd, want, step, line, nh, nkv, hd, window, scale, used, pps,
+        scratch = torch.empty(len(lens) * nh * splits * (hd + 2), device=DEV)
+        K.attention_decode(q, nh * hd, want, step, line, nh, nkv, hd, window, scale, splits,
                            scratch)
         got = torch.full_like(want, 7.0)
         allocated = torch.cuda.memory_allocated()
-        rc = call_static(fn, q, got, step, line, nh, nkv, hd, window, scale, used, pps)
+        rc = call_static(fn, q, got, step, line, nh, nkv, hd, window, scale, splits)
         assert rc == 0, lib.mb_last_error().decode()
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == allocated
@@ -79,12 +77,12 @@ def test_sizes_beyond_the_limit_are_refused():
     line, step, q = case(3, [10] * 64, nh, nkv, hd, 0)
     out = torch.full((64, nh * hd), 3.0, dtype=torch.bfloat16, device=DEV)
     assert 64 * nh * 16 * (hd + 2) > LIMIT
-    rc = call_static(fn, q, out, step, line, nh, nkv, hd, 0, 0.1, 16, 1)
+    rc = call_static(fn, q, out, step, line, nh, nkv, hd, 0, 0.1, 16)
     assert rc != 0
     message = lib.mb_last_error().decode()
     assert "scratch" in message and str(LIMIT) in message
     torch.cuda.synchronize()
     assert float(out.float().min()) == 3.0          # nothing was launched
     assert 64 * nh * 15 * (hd + 2) <= LIMIT         # the largest size still fits
-    assert call_static(fn, q, out, step, line, nh, nkv, hd, 0, 0.1, 15, 1) == 0
+    assert call_static(fn, q, out, step, line, nh, nkv, hd, 0, 0.1, 15) == 0
     torch.cuda.synchronize()
