@@ -45,7 +45,7 @@ enum { TC_STORE = 0, TC_ADD = 1, TC_PARTIAL = 2, TC_SWIGLU = 3 };
 
 template <int BN> struct TcCfg {
   static constexpr int B_BYTES = BN * TC_BK * 2;
-  static constexpr int COLS = BN < 32 ? 32 : BN;  // TMEM columns: a power of two >= 32
+  static constexpr int COLS = BN < 16 ? 16 : BN;  // TMEM columns of one accumulator (two are allocated)
 };
 
 __device__ __forceinline__ void store_out(void* C, int c_dtype, size_t idx, float v, int mode) {
@@ -68,8 +68,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                void* __restrict__ C, int c_dtype, long long ldc, int rowsA, int rowsB, int K,
                int kb_per_split, int mode, float* __restrict__ partial, long long partial_stride,
-               long long partial_ld, int tile_rows, int stages, int a_stage,
-               int* __restrict__ error) {
+               long long partial_ld, int tile_rows, int stages, int a_stage, int tiles_a,
+               int tiles_b, int num_tiles, int* __restrict__ error) {
   using Cfg = TcCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -80,15 +80,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t a_region = max(stages * a_stage, (stages - 1) * a_stage + TC_A_TILE);
   const uint32_t sB = base + a_region;
   const uint32_t bars = sB + stages * Cfg::B_BYTES;
-  const uint32_t full0 = bars, empty0 = bars + 8 * stages, accum = bars + 16 * stages;
-  const uint32_t slot = accum + 8;
+  const uint32_t full0 = bars, empty0 = bars + 8 * stages;
+  const uint32_t acc_full0 = bars + 16 * stages, acc_empty0 = acc_full0 + 16;
+  const uint32_t slot = acc_empty0 + 16;
   volatile uint32_t* slot_ptr = (volatile uint32_t*)(smem_raw + (slot - raw));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * tile_rows, n0 = blockIdx.y * BN;
   const int nkb_total = (K + TC_BK - 1) / TC_BK;
-  const int kb0 = blockIdx.z * kb_per_split;
-  const int nkb = min(kb_per_split, nkb_total - kb0);
+  const int tiles_ab = tiles_a * tiles_b;
   const uint32_t stage_bytes = (uint32_t)tile_rows * (TC_BK * 2) + Cfg::B_BYTES;
 
   if (threadIdx.x == 0) {
@@ -96,12 +95,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(accum, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_empty0 + 8 * b, 4);  // the four epilogue warps
+    }
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
   }
-  if (warp == 1) tmem_alloc(slot, Cfg::COLS);
+  if (warp == 1) tmem_alloc(slot, 2 * Cfg::COLS);  // two accumulators
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -111,16 +113,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   mb_grid_wait();
   mb_grid_launch_next();
 
+  // A CTA walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...: along the lanes' operand
+  // first, so that CTAs that run together share rows of the columns' operand in L2. The load
+  // warp runs ahead through the ring of stages; the MMA warp fills the two accumulators in
+  // turn, so that the epilogue of one tile overlaps the MMAs of the next.
   if (warp == 0) {
     if (elect_one()) {
       int s = 0;
       uint32_t ph = 0;
-      for (int i = 0; i < nkb; ++i) {
-        mbar_wait(empty0 + 8 * s, ph ^ 1, error, 1);
-        mbar_expect_tx(full0 + 8 * s, stage_bytes);
-        tma_load_2d(sA + s * a_stage, &tmA, (kb0 + i) * TC_BK, m0, full0 + 8 * s);
-        tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, (kb0 + i) * TC_BK, n0, full0 + 8 * s);
-        if (++s == stages) { s = 0; ph ^= 1; }
+      for (int w = blockIdx.x; w < num_tiles; w += gridDim.x) {
+        const int rem = w % tiles_ab;
+        const int m0 = (rem % tiles_a) * tile_rows, n0 = (rem / tiles_a) * BN;
+        const int kb0 = (w / tiles_ab) * kb_per_split;
+        const int nkb = min(kb_per_split, nkb_total - kb0);
+        for (int i = 0; i < nkb; ++i) {
+          mbar_wait(empty0 + 8 * s, ph ^ 1, error, 1);
+          mbar_expect_tx(full0 + 8 * s, stage_bytes);
+          tma_load_2d(sA + s * a_stage, &tmA, (kb0 + i) * TC_BK, m0, full0 + 8 * s);
+          tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, (kb0 + i) * TC_BK, n0, full0 + 8 * s);
+          if (++s == stages) { s = 0; ph ^= 1; }
+        }
       }
     }
   } else if (warp == 1) {
@@ -128,107 +140,127 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
       int s = 0;
       uint32_t ph = 0;
-      for (int i = 0; i < nkb; ++i) {
-        mbar_wait(full0 + 8 * s, ph, error, 2);
+      int it = 0;
+      for (int w = blockIdx.x; w < num_tiles; w += gridDim.x, ++it) {
+        const int kb0 = (w / tiles_ab) * kb_per_split;
+        const int nkb = min(kb_per_split, nkb_total - kb0);
+        const int b = it & 1;
+        mbar_wait(acc_empty0 + 8 * b, ((it >> 1) & 1) ^ 1, error, 6);  // the epilogue left it
         tc_fence_after_sync();
-        const uint64_t da = umma_desc_k128(sA + s * a_stage);
-        const uint64_t db = umma_desc_k128(sB + s * Cfg::B_BYTES);
+        const uint32_t acc = tmem + b * Cfg::COLS;
+        for (int i = 0; i < nkb; ++i) {
+          mbar_wait(full0 + 8 * s, ph, error, 2);
+          tc_fence_after_sync();
+          const uint64_t da = umma_desc_k128(sA + s * a_stage);
+          const uint64_t db = umma_desc_k128(sB + s * Cfg::B_BYTES);
 #pragma unroll
-        for (int k = 0; k < TC_BK / 16; ++k)  // 16 values of K = 32 bytes further in the row
-          umma_bf16(tmem, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
-        umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
-        if (++s == stages) { s = 0; ph ^= 1; }
+          for (int k = 0; k < TC_BK / 16; ++k)  // 16 values of K = 32 bytes further in the row
+            umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
+          umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
+          if (++s == stages) { s = 0; ph ^= 1; }
+        }
+        umma_commit(acc_full0 + 8 * b);
       }
-      umma_commit(accum);
     }
   } else {
-    mbar_wait(accum, 0, error, 3);
-    tc_fence_after_sync();
     const int q = warp & 3;  // the TMEM lanes a warp may read: 32 * (warp % 4) ..
     const int lane_row = q * 32 + lane;
-    const int a = m0 + lane_row;
-    const bool mine = lane_row < tile_rows && a < rowsA;
-    const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
-    float* part = partial ? partial + blockIdx.z * partial_stride : nullptr;
+    int it = 0;
+    for (int w = blockIdx.x; w < num_tiles; w += gridDim.x, ++it) {
+      const int rem = w % tiles_ab, z = w / tiles_ab;
+      const int m0 = (rem % tiles_a) * tile_rows, n0 = (rem / tiles_a) * BN;
+      const int b = it & 1;
+      mbar_wait(acc_full0 + 8 * b, (it >> 1) & 1, error, 3);
+      tc_fence_after_sync();
+      const int a = m0 + lane_row;
+      const bool mine = lane_row < tile_rows && a < rowsA;
+      const uint32_t taddr = tmem + b * Cfg::COLS + ((uint32_t)(q * 32) << 16);
+      float* part = partial ? partial + z * partial_stride : nullptr;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 16) {
-      if (n0 + c0 >= rowsB) break;  // uniform over the warp
-      float v[16];
-      tmem_ld16(taddr + c0, v);
-      if (SWAP && mode == TC_SWIGLU) {
-        // lanes 2i and 2i+1 hold gate and up of output feature (m0 + lane_row) / 2
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (n0 + c0 >= rowsB) break;  // uniform over the warp
+        float v[16];
+        tmem_ld16(taddr + c0, v);
+        if (SWAP && mode == TC_SWIGLU) {
+          // lanes 2i and 2i+1 hold gate and up of output feature (m0 + lane_row) / 2
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);
-          const int b = n0 + c0 + j;
-          if (mine && !(lane & 1) && b < rowsB)
-            ((__nv_bfloat16*)C)[(size_t)b * ldc + (a >> 1)] = __float2bfloat16_rn(silu_mul(v[j], up));
+          for (int j = 0; j < 16; ++j) {
+            const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);
+            const int bb = n0 + c0 + j;
+            if (mine && !(lane & 1) && bb < rowsB)
+              ((__nv_bfloat16*)C)[(size_t)bb * ldc + (a >> 1)] =
+                  __float2bfloat16_rn(silu_mul(v[j], up));
+          }
+          continue;
         }
-        continue;
-      }
-      if (!mine) continue;
-      if (!SWAP) {
-        const int b0 = n0 + c0;
-        const bool whole = b0 + 16 <= rowsB;
-        if (mode == TC_SWIGLU) {
-          // columns 2i and 2i+1 are gate and up of output feature (b0 + 2i) / 2
-          __nv_bfloat16* p = (__nv_bfloat16*)C + (size_t)a * ldc + (b0 >> 1);
-          if (whole && (ldc & 7) == 0 && ((uintptr_t)C & 15) == 0) {
-            __nv_bfloat162 h[4];
+        if (!mine) continue;
+        if (!SWAP) {
+          const int b0 = n0 + c0;
+          const bool whole = b0 + 16 <= rowsB;
+          if (mode == TC_SWIGLU) {
+            // columns 2i and 2i+1 are gate and up of output feature (b0 + 2i) / 2
+            __nv_bfloat16* p = (__nv_bfloat16*)C + (size_t)a * ldc + (b0 >> 1);
+            if (whole && (ldc & 7) == 0 && ((uintptr_t)C & 15) == 0) {
+              __nv_bfloat162 h[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]),
-                                           silu_mul(v[4 * j + 2], v[4 * j + 3]));
-            *(uint4*)p = *(uint4*)&h[0];
-          } else {
-            for (int j = 0; j < 16 && b0 + j + 1 < rowsB; j += 2)
-              p[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
-          }
-        } else if (mode == TC_PARTIAL) {
-          float* p = part + (size_t)a * partial_ld + b0;
-          if (whole && (partial_ld & 3) == 0 && (partial_stride & 3) == 0) {
-#pragma unroll
-            for (int j = 0; j < 16; j += 4)
-              *(float4*)(p + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          } else {
-            for (int j = 0; j < 16 && b0 + j < rowsB; ++j) p[j] = v[j];
-          }
-        } else if (c_dtype == MB_BF16 && whole && (ldc & 7) == 0 && ((uintptr_t)C & 15) == 0) {
-          __nv_bfloat162 h[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-          uint4* p = (uint4*)((__nv_bfloat16*)C + (size_t)a * ldc + b0);
-          p[0] = *(uint4*)&h[0];
-          p[1] = *(uint4*)&h[4];
-        } else if (c_dtype == MB_F32 && whole && (ldc & 3) == 0 && ((uintptr_t)C & 15) == 0) {
-          float4* p = (float4*)((float*)C + (size_t)a * ldc + b0);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            if (mode == TC_ADD) {
-              const float4 r = p[j];
-              o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+              for (int j = 0; j < 4; ++j)
+                h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]),
+                                             silu_mul(v[4 * j + 2], v[4 * j + 3]));
+              *(uint4*)p = *(uint4*)&h[0];
+            } else {
+              for (int j = 0; j < 16 && b0 + j + 1 < rowsB; j += 2)
+                p[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
             }
-            p[j] = o;
+          } else if (mode == TC_PARTIAL) {
+            float* p = part + (size_t)a * partial_ld + b0;
+            if (whole && (partial_ld & 3) == 0 && (partial_stride & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4)
+                *(float4*)(p + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+              for (int j = 0; j < 16 && b0 + j < rowsB; ++j) p[j] = v[j];
+            }
+          } else if (c_dtype == MB_BF16 && whole && (ldc & 7) == 0 && ((uintptr_t)C & 15) == 0) {
+            __nv_bfloat162 h[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            uint4* p = (uint4*)((__nv_bfloat16*)C + (size_t)a * ldc + b0);
+            p[0] = *(uint4*)&h[0];
+            p[1] = *(uint4*)&h[4];
+          } else if (c_dtype == MB_F32 && whole && (ldc & 3) == 0 && ((uintptr_t)C & 15) == 0) {
+            float4* p = (float4*)((float*)C + (size_t)a * ldc + b0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              if (mode == TC_ADD) {
+                const float4 r = p[j];
+                o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+              }
+              p[j] = o;
+            }
+          } else {
+            for (int j = 0; j < 16 && b0 + j < rowsB; ++j)
+              store_out(C, c_dtype, (size_t)a * ldc + b0 + j, v[j], mode);
           }
         } else {
-          for (int j = 0; j < 16 && b0 + j < rowsB; ++j)
-            store_out(C, c_dtype, (size_t)a * ldc + b0 + j, v[j], mode);
-        }
-      } else {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int b = n0 + c0 + j;
-          if (b >= rowsB) continue;
-          if (mode == TC_PARTIAL) part[(size_t)b * partial_ld + a] = v[j];
-          else store_out(C, c_dtype, (size_t)b * ldc + a, v[j], mode);
+          for (int j = 0; j < 16; ++j) {
+            const int bb = n0 + c0 + j;
+            if (bb >= rowsB) continue;
+            if (mode == TC_PARTIAL) part[(size_t)bb * partial_ld + a] = v[j];
+            else store_out(C, c_dtype, (size_t)bb * ldc + a, v[j], mode);
+          }
         }
       }
+      // this warp has read its lanes of the accumulator: the MMA warp may overwrite it
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty0 + 8 * b);
     }
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, Cfg::COLS);
+  if (warp == 1) tmem_dealloc(tmem, 2 * Cfg::COLS);
 }
 
 // C[M, N] = (or +=) the sum over the splits, added in split order
@@ -248,7 +280,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
 }
 
 struct TcPlan {
-  int tile_rows, stages, a_stage, smem, splits, kb_per_split;
+  int tile_rows, stages, a_stage, smem, splits, kb_per_split, max_ctas;
 };
 
 template <int BN, bool SWAP>
@@ -264,10 +296,12 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, in
                                   cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((rowsA + p.tile_rows - 1) / p.tile_rows, (rowsB + BN - 1) / BN, p.splits);
-  mb_launch(gemm_tc_kernel<BN, SWAP>, dim3(grid), dim3(TC_THREADS), p.smem, s, 
+  const int tiles_a = (rowsA + p.tile_rows - 1) / p.tile_rows, tiles_b = (rowsB + BN - 1) / BN;
+  const int num_tiles = tiles_a * tiles_b * p.splits;
+  const int grid = num_tiles < p.max_ctas ? num_tiles : p.max_ctas;
+  mb_launch(gemm_tc_kernel<BN, SWAP>, dim3(grid), dim3(TC_THREADS), p.smem, s,
       tmA, tmB, C, c_dtype, ldc, rowsA, rowsB, K, p.kb_per_split, mode, partial, pstride, pld,
-      p.tile_rows, p.stages, p.a_stage, error);
+      p.tile_rows, p.stages, p.a_stage, tiles_a, tiles_b, num_tiles, error);
   MB_CHECK_LAUNCH("mb_gemm_tc");
 }
 
@@ -335,6 +369,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
       rows += rows & 1;  // gate/up pairs stay in one tile
     }
     p.tile_rows = rows;
+    p.max_ctas = slots;
     plan_stages(p, bn, 110 * 1024);
     if (workspace && epilogue != TC_SWIGLU && tiles128 <= sms && nkb >= 8) {
       int want = slots / tiles128;
@@ -347,6 +382,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     p.splits = (nkb + p.kb_per_split - 1) / p.kb_per_split;
   } else {
     p.tile_rows = TC_BM;
+    p.max_ctas = sms;
     plan_stages(p, bn, 200 * 1024);
     const int tiles = ((rowsA + TC_BM - 1) / TC_BM) * ((rowsB + bn - 1) / bn);
     if (workspace && epilogue != TC_SWIGLU && tiles < sms && nkb >= 8) {
