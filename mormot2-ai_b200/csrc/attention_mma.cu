@@ -407,8 +407,70 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
 // query head; each of its four warps owns 16 of them as the rows of the MMA and walks the pages
 // from the first key its rows may see to the last, with an online softmax per row. The four
 // warps read the same pages, so all but the first read hit the L1 cache.
+// the same pieces as qk_page / pv_page with the page's tiles in shared memory
+template <int HD, int KP>
+__device__ __forceinline__ void qk_page_smem(const uint4* qa, const uint4* qb, uint32_t ks, int r,
+                                             int c, float sc[8][4]) {
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    sc[u][0] = sc[u][1] = sc[u][2] = sc[u][3] = 0.f;
+    const uint32_t krow = ks + (uint32_t)(u * 8 + r) * KP + c * 16;
+#pragma unroll
+    for (int ch = 0; ch < HD / 32; ++ch) {
+      const uint4 kb = lds16(krow + ch * 64);
+      mma_bf16(sc[u], qa[ch].x, qb[ch].x, qa[ch].y, qb[ch].y, kb.x, kb.y);
+      mma_bf16(sc[u], qa[ch].z, qb[ch].z, qa[ch].w, qb[ch].w, kb.z, kb.w);
+    }
+  }
+}
+
+template <int HD, int VP>
+__device__ __forceinline__ void pv_page_smem(const float sc[8][4], uint32_t vs, int r, int c,
+                                             float o[HD / 64][8][4]) {
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) {
+    const uint32_t a0 = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+    const uint32_t a1 = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+    const uint32_t a2 = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+    const uint32_t a3 = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+    const uint32_t vrow = vs + (uint32_t)(kk * 16 + 2 * c) * VP + r * 16;
+#pragma unroll
+    for (int db = 0; db < HD / 64; ++db) {
+      const uint4 va = lds16(vrow + db * 128);
+      const uint4 vb = lds16(vrow + VP + db * 128);
+      const uint4 vc = lds16(vrow + 8 * VP + db * 128);
+      const uint4 vd = lds16(vrow + 9 * VP + db * 128);
+      const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+      const uint32_t wc[4] = {vc.x, vc.y, vc.z, vc.w}, wd[4] = {vd.x, vd.y, vd.z, vd.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int w = j >> 1;
+        const uint32_t b0 = (j & 1) ? pack_hi(wa[w], wb[w]) : pack_lo(wa[w], wb[w]);
+        const uint32_t b1 = (j & 1) ? pack_hi(wc[w], wd[w]) : pack_lo(wc[w], wd[w]);
+        mma_bf16(o[db][j], a0, a1, a2, a3, b0, b1);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+#define PRE_STAGES 3
+
+// A CTA takes 64 consecutive new tokens of one sequence and one query head; each of its four
+// warps owns 16 tokens as the rows of the MMA and keeps an online softmax per row. The pages
+// that any of the CTA's tokens may see are brought to shared memory by all threads with 16-byte
+// asynchronous copies, two pages ahead of the page in work. The rows of a tile are padded in
+// shared memory (keys to a pitch of 2 HD + 64 bytes, values to 2 HD + 16), which makes every
+// fragment read of qk_page_smem / pv_page_smem free of bank conflicts.
 template <int HD>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(DEC_WARPS * 32, 2)
 attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                     int out_stride, const bf16* __restrict__ kpool,
                     const bf16* __restrict__ vpool, const int* __restrict__ page_table,
@@ -418,14 +480,43 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
   mb_grid_wait();
   mb_grid_launch_next();
   constexpr int CH = HD / 32, DB = HD / 64;
+  constexpr int KP = HD * 2 + 64, VP = HD * 2 + 16;     // row pitches in bytes
+  constexpr uint32_t STAGE = MB_PAGE * (KP + VP);
+  constexpr int CHUNKS = HD / 8;                        // 16-byte chunks of a row
+  extern __shared__ __align__(128) uint8_t pre_smem[];
+  const uint32_t tiles = smem_u32(pre_smem);
+
   const int b = blockIdx.z, h = blockIdx.y;
   const int start = seq_start[b], n_new = seq_start[b + 1] - start;
+  if ((int)blockIdx.x * 64 >= n_new) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane >> 2, c = lane & 3;
-  const int row0 = blockIdx.x * 64 + warp * 16;
-  if (row0 >= n_new) return;  // whole warps leave; nothing below synchronizes the CTA
   const int past = seq_past[b], slot = seq_slot[b];
   const int g = h / (nh / nkv);
+  // the pages that the CTA's tokens see: from the first token's first key to the last token
+  const int cta_first = past + blockIdx.x * 64;
+  const int cta_last = past + min((int)blockIdx.x * 64 + 63, n_new - 1);
+  const int cta_lo = (window > 0 && cta_first + 1 > window) ? cta_first + 1 - window : 0;
+  const int page0 = cta_lo / MB_PAGE, n_pages = cta_last / MB_PAGE - page0 + 1;
+
+  auto issue = [&](int i) {  // page i of the CTA into stage i % PRE_STAGES
+    if (i < n_pages) {
+      const int p = page0 + i;
+      const int page = page_table[(size_t)slot * max_pages + (ring_pages > 0 ? p % ring_pages : p)];
+      const bf16* ksrc = kpool + ((size_t)page * nkv + g) * MB_PAGE * HD;
+      const bf16* vsrc = vpool + ((size_t)page * nkv + g) * MB_PAGE * HD;
+      const uint32_t kd = tiles + (i % PRE_STAGES) * STAGE, vd = kd + MB_PAGE * KP;
+      for (int e = threadIdx.x; e < MB_PAGE * CHUNKS; e += DEC_WARPS * 32) {
+        const int row = e / CHUNKS, ch = e % CHUNKS;
+        cp_async16(kd + row * KP + ch * 16, ksrc + row * HD + ch * 8);
+        cp_async16(vd + row * VP + ch * 16, vsrc + row * HD + ch * 8);
+      }
+    }
+    cp_async_commit();
+  };
+
+  const int row0 = blockIdx.x * 64 + warp * 16;
+  const bool live = row0 < n_new;  // a warp without rows still loads and synchronizes
   const int ra = row0 + r, rb = ra + 8;
   const bool has_a = ra < n_new, has_b = rb < n_new;
   const int pa = past + ra, pb = past + rb;  // positions of the two rows
@@ -433,6 +524,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
   const int lb = (window > 0 && pb + 1 > window) ? pb + 1 - window : 0;
   const int first_pos = past + row0, last_pos = past + min(row0 + 15, n_new - 1);
   const int lo_w = (window > 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
+
+#pragma unroll
+  for (int i = 0; i < PRE_STAGES - 1; ++i) issue(i);
 
   uint4 qa[CH], qb[CH];
   {
@@ -448,60 +542,66 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
 #pragma unroll
       for (int e = 0; e < 4; ++e) o[db][j][e] = 0.f;
 
-  for (int p = lo_w / MB_PAGE; p <= last_pos / MB_PAGE; ++p) {
-    const int lp = ring_pages > 0 ? p % ring_pages : p;
-    const int page = page_table[(size_t)slot * max_pages + lp];
-    const bf16* kbase = kpool + ((size_t)page * nkv + g) * MB_PAGE * HD;
-    const bf16* vbase = vpool + ((size_t)page * nkv + g) * MB_PAGE * HD;
-    const int key0 = p * MB_PAGE;
-    float sc[8][4];
-    qk_page<HD>(qa, qb, kbase, r, c, sc);
-    float mx0 = -INFINITY, mx1 = -INFINITY;
+  for (int i = 0; i < n_pages; ++i) {
+    cp_async_wait<PRE_STAGES - 2>();  // page i has landed (for this thread's copies)
+    __syncthreads();                  // ... for everyone's; and page i - 1 has been read by all
+    issue(i + PRE_STAGES - 1);        // into the stage that page i - 1 occupied
+    const int p = page0 + i;
+    // the pages before this warp's window and after its last row are not its business
+    if (live && p >= lo_w / MB_PAGE && p <= last_pos / MB_PAGE) {
+      const uint32_t ks = tiles + (i % PRE_STAGES) * STAGE, vs = ks + MB_PAGE * KP;
+      const int key0 = p * MB_PAGE;
+      float sc[8][4];
+      qk_page_smem<HD, KP>(qa, qb, ks, r, c, sc);
+      float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
+      for (int u = 0; u < 8; ++u) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int key = key0 + u * 8 + 2 * c + e;
-        sc[u][e] = (key >= la && key <= pa) ? sc[u][e] * scale_log2 : -INFINITY;
-        sc[u][2 + e] = (key >= lb && key <= pb) ? sc[u][2 + e] * scale_log2 : -INFINITY;
-        mx0 = fmaxf(mx0, sc[u][e]);
-        mx1 = fmaxf(mx1, sc[u][2 + e]);
+        for (int e = 0; e < 2; ++e) {
+          const int key = key0 + u * 8 + 2 * c + e;
+          sc[u][e] = (key >= la && key <= pa) ? sc[u][e] * scale_log2 : -INFINITY;
+          sc[u][2 + e] = (key >= lb && key <= pb) ? sc[u][2 + e] * scale_log2 : -INFINITY;
+          mx0 = fmaxf(mx0, sc[u][e]);
+          mx1 = fmaxf(mx1, sc[u][2 + e]);
+        }
       }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+      // a row may have no key in this page (and none so far): keep exp2 away from inf - inf
+      const float base0 = n0 == -INFINITY ? 0.f : n0, base1 = n1 == -INFINITY ? 0.f : n1;
+      const float c0 = exp2f(m0 - base0), c1 = exp2f(m1 - base1);
+      m0 = n0;
+      m1 = n1;
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          sc[u][e] = exp2f(sc[u][e] - base0);
+          sc[u][2 + e] = exp2f(sc[u][2 + e] - base1);
+          s0 += sc[u][e];
+          s1 += sc[u][2 + e];
+        }
+      }
+      l0 = l0 * c0 + s0;
+      l1 = l1 * c1 + s1;
+#pragma unroll
+      for (int db = 0; db < DB; ++db)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[db][j][0] *= c0;
+          o[db][j][1] *= c0;
+          o[db][j][2] *= c1;
+          o[db][j][3] *= c1;
+        }
+      pv_page_smem<HD, VP>(sc, vs, r, c, o);
     }
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-    // a row may have no key in this page (and none so far): keep exp2 away from inf - inf
-    const float base0 = n0 == -INFINITY ? 0.f : n0, base1 = n1 == -INFINITY ? 0.f : n1;
-    const float c0 = exp2f(m0 - base0), c1 = exp2f(m1 - base1);
-    m0 = n0;
-    m1 = n1;
-    float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        sc[u][e] = exp2f(sc[u][e] - base0);
-        sc[u][2 + e] = exp2f(sc[u][2 + e] - base1);
-        s0 += sc[u][e];
-        s1 += sc[u][2 + e];
-      }
-    }
-    l0 = l0 * c0 + s0;
-    l1 = l1 * c1 + s1;
-#pragma unroll
-    for (int db = 0; db < DB; ++db)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        o[db][j][0] *= c0;
-        o[db][j][1] *= c0;
-        o[db][j][2] *= c1;
-        o[db][j][3] *= c1;
-      }
-    pv_page<HD>(sc, vbase, r, c, o);
   }
+  cp_async_wait<0>();
+  if (!live) return;
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -533,12 +633,12 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
 
 // out[t, h, :] for the new tokens of B sequences (packed one after another: sequence b holds
 // the rows seq_start[b] .. seq_start[b + 1]) over the cache. `max_new`: the most new tokens of
-// one sequence.
+// one sequence. `error`: a device word that receives 4 or 5 if a wait of the copy pipeline ran out.
 MB_EXPORT int mb_attention_prefill(const void* q, int q_stride, void* out, int out_stride,
                                    const void* kpool, const void* vpool, const int* page_table,
                                    int max_pages, int ring_pages, const int* seq_start,
                                    const int* seq_past, const int* seq_slot, int B, int max_new,
-                                   int nh, int nkv, int hd, int window, float scale,
+                                   int nh, int nkv, int hd, int window, float scale, int* error,
                                    void* stream) {
   if (B <= 0 || max_new <= 0) return 0;
   if (hd != 64 && hd != 128)
@@ -551,16 +651,24 @@ MB_EXPORT int mb_attention_prefill(const void* q, int q_stride, void* out, int o
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid((max_new + 63) / 64, nh, B);
   const float scale_log2 = scale * 1.4426950408889634f;
-  if (hd == 64)
-    mb_launch(attn_prefill_kernel<64>, dim3(grid), dim3(128), 0, s, 
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kpool, (const bf16*)vpool,
-        page_table, max_pages, ring_pages, seq_start, seq_past, seq_slot, nh, nkv, window,
-        scale_log2);
-  else
-    mb_launch(attn_prefill_kernel<128>, dim3(grid), dim3(128), 0, s, 
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kpool, (const bf16*)vpool,
-        page_table, max_pages, ring_pages, seq_start, seq_past, seq_slot, nh, nkv, window,
-        scale_log2);
+#define GO(HD_)                                                                                \
+  {                                                                                            \
+    constexpr int smem = PRE_STAGES * MB_PAGE * (4 * HD_ + 80);                                \
+    static bool configured = false;                                                            \
+    if (!configured) {                                                                         \
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD_>,                           \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+      if (e != cudaSuccess) MB_FAIL("mb_attention_prefill: %s", cudaGetErrorString(e));        \
+      configured = true;                                                                       \
+    }                                                                                          \
+    mb_launch(attn_prefill_kernel<HD_>, grid, dim3(DEC_WARPS * 32), smem, s, (const bf16*)q,   \
+              q_stride, (bf16*)out, out_stride, (const bf16*)kpool, (const bf16*)vpool,        \
+              page_table, max_pages, ring_pages, seq_start, seq_past, seq_slot, nh, nkv,       \
+              window, scale_log2);                                                             \
+  }
+  if (hd == 64) GO(64) else GO(128)
+#undef GO
+  (void)error;
   MB_CHECK_LAUNCH("mb_attention_prefill");
 }
 

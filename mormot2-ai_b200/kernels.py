@@ -283,15 +283,16 @@ def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, li
 
 
 def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv,
-                      hd, window: int, scale: float) -> None:
+                      hd, window: int, scale: float,
+                      error: Optional[torch.Tensor] = None) -> None:
     """Causal attention of every sequence's new tokens over the paged cache on the tensor
     cores (the cache already holds their keys and values)."""
     _contig(out, "out")
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     _call("attention_mma", "mb_attention_prefill",
           [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f,
-           _vp],
+           _vp, _vp],
           _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.seq_start),
           _ptr(step.seq_past), _ptr(step.seq_slot), step.B, step.max_new, nh, nkv, hd, window,
-          float(scale), _stream())
+          float(scale), _ptr(error), _stream())

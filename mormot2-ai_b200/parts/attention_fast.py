@@ -40,5 +40,6 @@ def run(rt, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> bool:
         return True
     if out.stride(0) % 8 or out.data_ptr() % 16:
         return False
-    K.attention_prefill(q, q_stride, out, step, line, nh, nkv, hd, window, scale)
+    K.attention_prefill(q, q_stride, out, step, line, nh, nkv, hd, window, scale,
+                        rt.error_word)
     return True
