@@ -115,8 +115,6 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const int* __restrict__ tok_pos, const int* __restrict__ seq_slot, int nh,
                    int nkv, int window, float scale_log2, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int* __restrict__ error) {
-  mb_grid_wait();
-  mb_grid_launch_next();
   constexpr int CH = HD / 32;  // 32-dim chunks of q·k
   constexpr int DB = HD / 64;  // 64-dim blocks of p·v
   constexpr uint32_t TILE = MB_PAGE * HD * 2;  // bytes of a page's keys (or values)
@@ -160,7 +158,12 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
       for (int e = 0; e < 4; ++e) o[db][j][e] = 0.f;
 
   if (warp == DEC_WARPS) {
-    // producer: the lanes fetch the ids of up to 32 pages at once, lane 0 issues the copies
+    // producer: the lanes fetch the ids of up to 32 pages at once, lane 0 issues the copies.
+    // Only the page that holds the newest position is written by the kernel before this one
+    // (the index arrays and all older pages were settled long before): the copies of the older
+    // pages start at once, the wait for that kernel comes before the first copy of the newest
+    // page (and at the latest at the end).
+    bool waited = false;
     int st = 0;
     uint32_t ph = 0;
     for (int i0 = 0; i0 < n_pages; i0 += 32) {
@@ -172,6 +175,10 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
       const int n = min(32, n_pages - i0);
       for (int i = 0; i < n; ++i) {
         const int page = __shfl_sync(0xffffffffu, mine, i);
+        if (!waited && p_first + (i0 + i) * S == p_last) {
+          mb_grid_wait();
+          waited = true;
+        }
         if (lane == 0) {
           mbar_wait(empty0 + 8 * st, ph ^ 1, error, 4);
           mbar_expect_tx(full0 + 8 * st, 2 * TILE);
@@ -182,7 +189,10 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
         if (++st == DEC_STAGES) { st = 0; ph ^= 1; }
       }
     }
+    if (!waited) mb_grid_wait();
+    mb_grid_launch_next();
   } else {
+    mb_grid_wait();  // q comes from the kernel before
     uint4 qa[CH], qb[CH];
     {
       const bf16* qrow = q + (size_t)t * q_stride + (size_t)(h0 + r) * HD;

@@ -40,9 +40,7 @@ static thread_local char g_mb_error[512];
 // lets the next kernel's CTAs be placed as soon as all CTAs of this one have started.
 __device__ __forceinline__ void mb_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void mb_grid_launch_next() {
-#ifdef MB_PDL_EARLY
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-#endif
 }
 
 static bool mb_pdl_enabled() {

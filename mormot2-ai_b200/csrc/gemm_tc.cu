@@ -108,34 +108,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *slot_ptr;
-  // everything above touched only this CTA's shared and tensor memory; from here on the
-  // kernels before in the stream must have finished
-  mb_grid_wait();
-  mb_grid_launch_next();
-
-  // A CTA walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...: along the lanes' operand
-  // first, so that CTAs that run together share rows of the columns' operand in L2. The load
-  // warp runs ahead through the ring of stages; the MMA warp fills the two accumulators in
-  // turn, so that the epilogue of one tile overlaps the MMAs of the next.
+  // Everything above touched only this CTA's shared and tensor memory. What follows may run
+  // while the kernel before in the stream is still at work (programmatic dependent launch):
+  // each role waits for that kernel (mb_grid_wait) before it touches memory that depends on it.
+  // In the decode form the lanes' operand is the WEIGHT, which depends on nothing: the load
+  // warp fills the first round of stages with weight tiles before it waits, so the small
+  // kernels between two products run under the stream of the next product's weights.
   if (warp == 0) {
     if (elect_one()) {
       int s = 0;
       uint32_t ph = 0;
+      int early = 0;
+      if (SWAP && (int)blockIdx.x < num_tiles) {
+        const int w = blockIdx.x, rem = w % tiles_ab;
+        const int m0 = (rem % tiles_a) * tile_rows;
+        const int kb0 = (w / tiles_ab) * kb_per_split;
+        early = min(stages, min(kb_per_split, nkb_total - kb0));
+        for (int i = 0; i < early; ++i) {
+          mbar_expect_tx(full0 + 8 * i, stage_bytes);
+          tma_load_2d(sA + i * a_stage, &tmA, (kb0 + i) * TC_BK, m0, full0 + 8 * i);
+        }
+      }
+      mb_grid_wait();
+      mb_grid_launch_next();
       for (int w = blockIdx.x; w < num_tiles; w += gridDim.x) {
         const int rem = w % tiles_ab;
         const int m0 = (rem % tiles_a) * tile_rows, n0 = (rem / tiles_a) * BN;
         const int kb0 = (w / tiles_ab) * kb_per_split;
         const int nkb = min(kb_per_split, nkb_total - kb0);
         for (int i = 0; i < nkb; ++i) {
-          mbar_wait(empty0 + 8 * s, ph ^ 1, error, 1);
-          mbar_expect_tx(full0 + 8 * s, stage_bytes);
-          tma_load_2d(sA + s * a_stage, &tmA, (kb0 + i) * TC_BK, m0, full0 + 8 * s);
+          if (early > 0) {
+            --early;  // this stage's barrier is armed and its weight tile is on the way
+          } else {
+            mbar_wait(empty0 + 8 * s, ph ^ 1, error, 1);
+            mbar_expect_tx(full0 + 8 * s, stage_bytes);
+            tma_load_2d(sA + s * a_stage, &tmA, (kb0 + i) * TC_BK, m0, full0 + 8 * s);
+          }
           tma_load_2d(sB + s * Cfg::B_BYTES, &tmB, (kb0 + i) * TC_BK, n0, full0 + 8 * s);
           if (++s == stages) { s = 0; ph ^= 1; }
         }
       }
+    } else {
+      mb_grid_wait();
     }
   } else if (warp == 1) {
+    mb_grid_wait();
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
       int s = 0;
@@ -163,6 +180,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else {
+    mb_grid_wait();
     const int q = warp & 3;  // the TMEM lanes a warp may read: 32 * (warp % 4) ..
     const int lane_row = q * 32 + lane;
     int it = 0;
