@@ -10,7 +10,8 @@ import pytest
 from tests.plain import qwen3_plain as plain
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REFERENCE_FIXTURES = "/root/reference/tests/data/infer-ref"
+# the reference project's tests/data/infer-ref folder, when a checkout of it is at hand
+REFERENCE_FIXTURES = os.environ.get("MORMOT_REFERENCE_FIXTURES", "")
 
 
 def test_golden_record_against_the_reference_fixtures():
@@ -26,7 +27,8 @@ def test_golden_record_against_the_reference_fixtures():
             assert max(r["max_abs_diff"].values()) < 5e-6, (name, case, r["max_abs_diff"])
 
 
-@pytest.mark.skipif(not os.path.isdir(REFERENCE_FIXTURES), reason="no reference tree here")
+@pytest.mark.skipif(not os.path.isdir(REFERENCE_FIXTURES),
+                    reason="set MORMOT_REFERENCE_FIXTURES to the reference's tests/data/infer-ref")
 def test_plain_matches_the_reference_fixtures_now():
     import hashlib
     for name in ("tiny-qwen3", "tiny-qwen3-sliding"):
