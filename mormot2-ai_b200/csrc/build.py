@@ -39,9 +39,12 @@ SOURCES = {
     "sampling": "sampling.cu",
     "gemm_tc": "gemm_tc.cu",
     "attention_mma": "attention_mma.cu",
+    "attention_tc": "attention_tc.cu",
 }
 HEADERS = ["common.cuh"]
-EXTRA_HEADERS = {"gemm_tc": ["tc_common.cuh"], "attention_mma": ["mma_common.cuh", "no_alloc.h"]}
+EXTRA_HEADERS = {"gemm_tc": ["tc_common.cuh"],
+                 "attention_mma": ["mma_common.cuh", "tc_common.cuh", "no_alloc.h"],
+                 "attention_tc": ["tc_common.cuh"]}
 
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}

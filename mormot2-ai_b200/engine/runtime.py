@@ -44,7 +44,7 @@ class Runtime:
         """The kernel libraries that a model of this runtime needs."""
         libs = ["elementwise", "gemm_simt", "attention_simt", "sampling"]
         if self.fast_kernels:
-            libs += ["gemm_tc", "attention_mma"]
+            libs += ["gemm_tc", "attention_mma", "attention_tc"]
         return libs
 
     def attention(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> None:

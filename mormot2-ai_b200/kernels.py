@@ -296,3 +296,19 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, l
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.seq_start),
           _ptr(step.seq_past), _ptr(step.seq_slot), step.B, step.max_new, nh, nkv, hd, window,
           float(scale), _ptr(error), _stream())
+
+
+def attention_prefill_tc(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv,
+                         hd, window: int, scale: float, error: torch.Tensor) -> None:
+    """The prefill attention on tcgen05 (heads of 128 values): S and O in tensor memory, Q, K
+    and V tiles by TMA."""
+    _contig(out, "out")
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and q.stride(1) == 1
+    pool_rows = line.k.shape[0] * line.k.shape[1] * line.k.shape[2]
+    _call("attention_tc", "mb_attention_prefill_tc",
+          [_vp, _i, _i, _vp, _i, _vp, _vp, _ll, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+           _i, _i, _f, _vp, _vp],
+          _ptr(q), q_stride, nh * hd, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
+          pool_rows, _ptr(line.page_table), line.max_pages, line.ring_pages,
+          _ptr(step.seq_start), _ptr(step.seq_past), _ptr(step.seq_slot), step.B, q.shape[0],
+          step.max_new, nh, nkv, hd, window, float(scale), _ptr(error), _stream())

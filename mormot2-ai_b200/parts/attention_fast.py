@@ -40,6 +40,11 @@ def run(rt, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> bool:
         return True
     if out.stride(0) % 8 or out.data_ptr() % 16:
         return False
+    if hd == 128 and q.stride(1) == 1:
+        # S and O in tensor memory, tiles by TMA (csrc/attention_tc.cu)
+        K.attention_prefill_tc(q, q_stride, out, step, line, nh, nkv, hd, window, scale,
+                               rt.error_word)
+        return True
     K.attention_prefill(q, q_stride, out, step, line, nh, nkv, hd, window, scale,
                         rt.error_word)
     return True

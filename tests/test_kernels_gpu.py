@@ -173,6 +173,11 @@ def run_attention(kind, q, out, step, line, nh, nkv, hd, window, scale, splits=N
     if kind == "prefill":
         K.attention_prefill(q, nh * hd, out, step, line, nh, nkv, hd, window, scale)
         return
+    if kind == "prefill_tc":
+        error = torch.zeros(1, dtype=torch.int32, device=DEV)
+        K.attention_prefill_tc(q, nh * hd, out, step, line, nh, nkv, hd, window, scale, error)
+        assert int(error.item()) == 0
+        return
     splits = splits or 3
     scratch = torch.empty(out.shape[0] * nh * splits * (hd + 2) + 5, device=DEV)
     error = torch.zeros(1, dtype=torch.int32, device=DEV)
@@ -189,7 +194,9 @@ ATTENTION_CASES = [("simt", 4, 2, 16, "float32"), ("simt", 6, 1, 48, "float32"),
                    ("decode", 3, 3, 64, "bfloat16"), ("decode", 40, 2, 128, "bfloat16"),
                    ("decode", 7, 1, 128, "bfloat16"),
                    ("prefill", 8, 2, 128, "bfloat16"), ("prefill", 16, 2, 64, "bfloat16"),
-                   ("prefill", 3, 3, 64, "bfloat16"), ("prefill", 7, 1, 128, "bfloat16")]
+                   ("prefill", 3, 3, 64, "bfloat16"), ("prefill", 7, 1, 128, "bfloat16"),
+                   ("prefill_tc", 8, 2, 128, "bfloat16"), ("prefill_tc", 7, 1, 128, "bfloat16"),
+                   ("prefill_tc", 3, 3, 128, "bfloat16")]
 
 
 @pytest.mark.parametrize("kind,nh,nkv,hd,dtype", ATTENTION_CASES)
@@ -230,7 +237,8 @@ def test_attention_over_the_paged_cache(kind, nh, nkv, hd, dtype):
 
 @pytest.mark.parametrize("kind,hd,dtype", [("simt", 32, "float32"), ("simt", 32, "bfloat16"),
                                            ("decode", 64, "bfloat16"), ("decode", 128, "bfloat16"),
-                                           ("prefill", 64, "bfloat16"), ("prefill", 128, "bfloat16")])
+                                           ("prefill", 64, "bfloat16"), ("prefill", 128, "bfloat16"),
+                                           ("prefill_tc", 128, "bfloat16")])
 def test_attention_finds_a_far_key_and_respects_the_windows_edge(kind, hd, dtype):
     """One key among 700 matches the query: the output must be that key's value. With a window,
     the matching key just inside the edge is found and the one just outside is not."""
@@ -378,8 +386,9 @@ def test_vocab_limit_is_never_crossed():
             assert all(t < 50 for t in sampler.pick(logits.to(DEV), slots, s, 50).tolist())
 
 
+@pytest.mark.parametrize("kind", ["prefill", "prefill_tc"])
 @pytest.mark.parametrize("window", [0, 150])
-def test_prefill_attention_of_long_unequal_prompts(window):
+def test_prefill_attention_of_long_unequal_prompts(window, kind):
     """The tensor-core prefill kernel over whole prompts of unequal lengths that cross several
     pages (65, 300, 1 and 129 tokens; the second one continues 70 cached positions)."""
     nh, nkv, hd = 4, 2, 128
@@ -398,7 +407,7 @@ def test_prefill_attention_of_long_unequal_prompts(window):
     q = torch.tensor(rng.standard_normal((T, nh * hd)), dtype=torch.float32).bfloat16()
     out = torch.zeros(T, nh * hd, dtype=torch.bfloat16, device=DEV)
     scale = 1 / math.sqrt(hd)
-    K.attention_prefill(q.to(DEV), nh * hd, out, step, line, nh, nkv, hd, window, scale)
+    run_attention(kind, q.to(DEV), out, step, line, nh, nkv, hd, window, scale)
     got = out.float().cpu().numpy().reshape(T, nh, hd)
     row = 0
     for (k, v), p, n in zip(kv, past, new):
