@@ -218,6 +218,10 @@ def main():
               "(this library has no multi-GPU path)")
         return 2
     a.warmup = max(a.warmup, 3)
+    if a.steps < 1 or a.steps + a.warmup > CONTEXT - 64:
+        print(f"bench.py: --steps + --warmup must leave a prompt of at least 64 tokens in the "
+              f"context of {CONTEXT}")
+        return 2
     import torch
     from mormot2_ai_b200 import Engine
     from mormot2_ai_b200.sampling import DeviceSampler, Sampling

@@ -45,8 +45,18 @@ def tiny_c():
                        rope_theta=5e5, tie_word_embeddings=True, layer_windows=(70, 0))
 
 
+def tiny_d():
+    """Heads of 128 values (the size of the tcgen05 attention kernel), three query heads on one
+    KV head, a hidden size below the q width, a window of 100 in the second layer."""
+    from mormot2_ai_b200 import Qwen3Config
+    return Qwen3Config(vocab_size=320, hidden_size=192, num_hidden_layers=2,
+                       num_attention_heads=3, num_key_value_heads=1, head_dim=128,
+                       intermediate_size=256, max_position_embeddings=384, rms_norm_eps=1e-6,
+                       rope_theta=1e4, tie_word_embeddings=False, layer_windows=(0, 100))
+
+
 TINY = {"A": (tiny_a, 0, 0.02, [5, 11, 17], 8), "B": (tiny_b, 1, 0.03, [1, 7, 30, 64], 12),
-        "C": (tiny_c, 2, 0.04, [3, 66, 129], 6)}
+        "C": (tiny_c, 2, 0.04, [3, 66, 129], 6), "D": (tiny_d, 3, 0.04, [2, 130, 200], 5)}
 
 
 class TinyModel:
@@ -68,7 +78,7 @@ class TinyModel:
         return self.plain.forward(self.plain_config, self.plain_weights, ids)
 
 
-@pytest.fixture(scope="session", params=["A", "B", "C"])
+@pytest.fixture(scope="session", params=["A", "B", "C", "D"])
 def tiny(request, tmp_path_factory):
     return TinyModel(request.param, str(tmp_path_factory.mktemp("tiny_" + request.param)))
 

@@ -60,10 +60,14 @@ def test_unequal_batches_with_slot_reuse(tiny, dtype):
     """Three slots and few pages for seven requests: batches of unequal lengths, the prompts in
     one step, then one token each; a request that ends leaves the batch and its slot and pages
     serve the next batch."""
-    eng = engine_of(tiny, dtype, max_tokens=448, max_slots=3)
     limit = tiny.config.max_position_embeddings
     lens = tiny.prompt_lens + [2, 65, 33, limit - tiny.decode_steps - 1]
     decode = [tiny.decode_steps, 3, 1, tiny.decode_steps, 5, 2, tiny.decode_steps][:len(lens)]
+    lens = lens[:len(decode)]
+    # just the pages that the fullest batch of three needs: later batches must reuse them
+    pages = max(sum(-(-(n + d) // 64) for n, d in list(zip(lens, decode))[b0:b0 + 3])
+                for b0 in range(0, len(lens), 3))
+    eng = engine_of(tiny, dtype, max_tokens=64 * pages, max_slots=3)
     reqs = [tiny.tokens(n + d, seed=200 + i) for i, (n, d) in enumerate(zip(lens, decode))]
     refs = [tiny.reference(r) for r in reqs]
     used_slots = []
