@@ -59,6 +59,59 @@ __device__ __forceinline__ void store_out(void* C, int c_dtype, size_t idx, floa
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
+// Sixteen neighbouring columns b0 .. b0 + 15 of accumulator row `a` in the prefill form
+// (tokens on the lanes): store, add into the residual, leave as a partial sum, or SwiGLU.
+__device__ __forceinline__ void store_row16(const float* v, void* C, int c_dtype, long long ldc,
+                                            int a, int b0, int rowsB, int mode, float* part,
+                                            long long partial_ld, long long partial_stride) {
+  const bool whole = b0 + 16 <= rowsB;
+  if (mode == TC_SWIGLU) {
+    // columns 2i and 2i+1 are gate and up of output feature (b0 + 2i) / 2
+    __nv_bfloat16* p = (__nv_bfloat16*)C + (size_t)a * ldc + (b0 >> 1);
+    if (whole && (ldc & 7) == 0 && ((uintptr_t)C & 15) == 0) {
+      __nv_bfloat162 h[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]),
+                                     silu_mul(v[4 * j + 2], v[4 * j + 3]));
+      *(uint4*)p = *(uint4*)&h[0];
+    } else {
+      for (int j = 0; j < 16 && b0 + j + 1 < rowsB; j += 2)
+        p[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+    }
+  } else if (mode == TC_PARTIAL) {
+    float* p = part + (size_t)a * partial_ld + b0;
+    if (whole && (partial_ld & 3) == 0 && (partial_stride & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 4)
+        *(float4*)(p + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+      for (int j = 0; j < 16 && b0 + j < rowsB; ++j) p[j] = v[j];
+    }
+  } else if (c_dtype == MB_BF16 && whole && (ldc & 7) == 0 && ((uintptr_t)C & 15) == 0) {
+    __nv_bfloat162 h[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    uint4* p = (uint4*)((__nv_bfloat16*)C + (size_t)a * ldc + b0);
+    p[0] = *(uint4*)&h[0];
+    p[1] = *(uint4*)&h[4];
+  } else if (c_dtype == MB_F32 && whole && (ldc & 3) == 0 && ((uintptr_t)C & 15) == 0) {
+    float4* p = (float4*)((float*)C + (size_t)a * ldc + b0);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      if (mode == TC_ADD) {
+        const float4 r = p[j];
+        o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+      }
+      p[j] = o;
+    }
+  } else {
+    for (int j = 0; j < 16 && b0 + j < rowsB; ++j)
+      store_out(C, c_dtype, (size_t)a * ldc + b0 + j, v[j], mode);
+  }
+}
+
 // rowsA x rowsB outputs: element (a, b) is the dot product of row a of the lanes' operand and
 // row b of the columns' operand. SWAP false: C[a * ldc + b]; true: C[b * ldc + a].
 // A CTA owns `tile_rows` (<= 128) rows of the lanes' operand; its stages hold a_stage bytes of
@@ -213,53 +266,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         if (!mine) continue;
         if (!SWAP) {
-          const int b0 = n0 + c0;
-          const bool whole = b0 + 16 <= rowsB;
-          if (mode == TC_SWIGLU) {
-            // columns 2i and 2i+1 are gate and up of output feature (b0 + 2i) / 2
-            __nv_bfloat16* p = (__nv_bfloat16*)C + (size_t)a * ldc + (b0 >> 1);
-            if (whole && (ldc & 7) == 0 && ((uintptr_t)C & 15) == 0) {
-              __nv_bfloat162 h[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]),
-                                             silu_mul(v[4 * j + 2], v[4 * j + 3]));
-              *(uint4*)p = *(uint4*)&h[0];
-            } else {
-              for (int j = 0; j < 16 && b0 + j + 1 < rowsB; j += 2)
-                p[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
-            }
-          } else if (mode == TC_PARTIAL) {
-            float* p = part + (size_t)a * partial_ld + b0;
-            if (whole && (partial_ld & 3) == 0 && (partial_stride & 3) == 0) {
-#pragma unroll
-              for (int j = 0; j < 16; j += 4)
-                *(float4*)(p + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-              for (int j = 0; j < 16 && b0 + j < rowsB; ++j) p[j] = v[j];
-            }
-          } else if (c_dtype == MB_BF16 && whole && (ldc & 7) == 0 && ((uintptr_t)C & 15) == 0) {
-            __nv_bfloat162 h[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-            uint4* p = (uint4*)((__nv_bfloat16*)C + (size_t)a * ldc + b0);
-            p[0] = *(uint4*)&h[0];
-            p[1] = *(uint4*)&h[4];
-          } else if (c_dtype == MB_F32 && whole && (ldc & 3) == 0 && ((uintptr_t)C & 15) == 0) {
-            float4* p = (float4*)((float*)C + (size_t)a * ldc + b0);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-              if (mode == TC_ADD) {
-                const float4 r = p[j];
-                o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
-              }
-              p[j] = o;
-            }
-          } else {
-            for (int j = 0; j < 16 && b0 + j < rowsB; ++j)
-              store_out(C, c_dtype, (size_t)a * ldc + b0 + j, v[j], mode);
-          }
+          store_row16(v, C, c_dtype, ldc, a, n0 + c0, rowsB, mode, part, partial_ld,
+                      partial_stride);
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -279,6 +287,200 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 2 * Cfg::COLS);
+}
+
+// ---------------------------------------------------------------------------- CTA pairs
+// The prefill form for many tokens: two CTAs of a cluster share one tile of 256 tokens x 256
+// output features. Each loads its 128 token rows and its 128 of the 256 weight rows (half the
+// shared-memory traffic of two separate 128 x 256 tiles, so six stages of 32 KB fit instead of
+// four of 48 KB), rank 0 issues tcgen05.mma.cta_group::2 for both, and each CTA's epilogue
+// warps read the 128 accumulator lanes that landed in its own tensor memory.
+//   full[s]      in rank 0: both CTAs' TMA loads complete their bytes there
+//   empty[s]     in both:   a multicast commit of rank 0's MMA thread frees the stage in both
+//   acc_full[b]  in both:   multicast commit after a tile's last MMA
+//   acc_empty[b] in rank 0: the eight epilogue warps of the pair arrive (rank 1's from afar)
+#define TC2_BN 256
+#define TC2_HALF (128 * TC_BK * 2)  // one CTA's share of either operand in a stage
+#define TC2_STAGES 6
+#define TC2_COLS 256
+#define TC2_SMEM (1024 + TC2_STAGES * 2 * TC2_HALF + 1024)
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    void* __restrict__ C, int c_dtype, long long ldc, int M, int N, int K,
+                    int kb_per_split, int mode, float* __restrict__ partial,
+                    long long partial_stride, long long partial_ld, int tiles_m, int tiles_n,
+                    int num_tiles, int* __restrict__ error) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t sA = base, sB = base + TC2_STAGES * TC2_HALF;
+  const uint32_t bars = sB + TC2_STAGES * TC2_HALF;
+  const uint32_t full0 = bars, empty0 = bars + 8 * TC2_STAGES;
+  const uint32_t acc_full0 = bars + 16 * TC2_STAGES, acc_empty0 = acc_full0 + 16;
+  const uint32_t slot = acc_empty0 + 16;
+  volatile uint32_t* slot_ptr = (volatile uint32_t*)(smem_raw + (slot - raw));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int nkb_total = (K + TC_BK - 1) / TC_BK;
+  const int tiles_mn = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TC2_STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_empty0 + 8 * b, 8);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) tmem_alloc_pair(slot, 2 * TC2_COLS);
+  tc_fence_before_sync();
+  cluster_sync_all();  // both CTAs' barriers and tensor memory exist before either is used
+  tc_fence_after_sync();
+  const uint32_t tmem = *slot_ptr;
+
+  mb_grid_wait();
+  mb_grid_launch_next();
+  if (warp == 0) {
+    if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int w = pair; w < num_tiles; w += pairs) {
+        const int rem = w % tiles_mn;
+        const int m0 = (rem % tiles_m) * 256 + (int)rank * 128;
+        const int n0 = (rem / tiles_m) * TC2_BN + (int)rank * 128;
+        const int kb0 = (w / tiles_mn) * kb_per_split;
+        const int nkb = min(kb_per_split, nkb_total - kb0);
+        for (int i = 0; i < nkb; ++i) {
+          mbar_wait(empty0 + 8 * s, ph ^ 1, error, 11);
+          if (rank == 0) mbar_expect_tx(full0 + 8 * s, 4 * TC2_HALF);
+          const uint32_t full_lead = cluster_addr_of(full0 + 8 * s, 0);
+          tma_load_2d_pair(sA + s * TC2_HALF, &tmA, (kb0 + i) * TC_BK, m0, full_lead);
+          tma_load_2d_pair(sB + s * TC2_HALF, &tmB, (kb0 + i) * TC_BK, n0, full_lead);
+          if (++s == TC2_STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (rank == 0 && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(256, TC2_BN);
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      for (int w = pair; w < num_tiles; w += pairs, ++it) {
+        const int kb0 = (w / tiles_mn) * kb_per_split;
+        const int nkb = min(kb_per_split, nkb_total - kb0);
+        const int b = it & 1;
+        mbar_wait(acc_empty0 + 8 * b, ((it >> 1) & 1) ^ 1, error, 16);
+        tc_fence_after_sync();
+        const uint32_t acc = tmem + b * TC2_COLS;
+        for (int i = 0; i < nkb; ++i) {
+          mbar_wait(full0 + 8 * s, ph, error, 12);
+          tc_fence_after_sync();
+          const uint64_t da = umma_desc_k128(sA + s * TC2_HALF);
+          const uint64_t db = umma_desc_k128(sB + s * TC2_HALF);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k)
+            umma_bf16_pair(acc, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
+          umma_commit_pair(empty0 + 8 * s, 3);
+          if (++s == TC2_STAGES) { s = 0; ph ^= 1; }
+        }
+        umma_commit_pair(acc_full0 + 8 * b, 3);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int lane_row = q * 32 + lane;
+    int it = 0;
+    for (int w = pair; w < num_tiles; w += pairs, ++it) {
+      const int rem = w % tiles_mn, z = w / tiles_mn;
+      const int n0 = (rem / tiles_m) * TC2_BN;
+      const int a = (rem % tiles_m) * 256 + (int)rank * 128 + lane_row;
+      const int b = it & 1;
+      mbar_wait(acc_full0 + 8 * b, (it >> 1) & 1, error, 13);
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem + b * TC2_COLS + ((uint32_t)(q * 32) << 16);
+      float* part = partial ? partial + z * partial_stride : nullptr;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TC2_BN; c0 += 16) {
+        if (n0 + c0 >= N) break;
+        float v[16];
+        tmem_ld16(taddr + c0, v);
+        if (a < M)
+          store_row16(v, C, c_dtype, ldc, a, n0 + c0, N, mode, part, partial_ld, partial_stride);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(acc_empty0 + 8 * b);
+        else mbar_arrive_cluster(cluster_addr_of(acc_empty0 + 8 * b, 0));
+      }
+    }
+  }
+  // Neither CTA leaves while the other may still read its shared memory or signal its barriers.
+  tc_fence_before_sync();
+  cluster_sync_all();
+  if (warp == 1) tmem_dealloc_pair(tmem, 2 * TC2_COLS);
+}
+
+// How many CTA pairs the device runs at once (0: the pair kernel cannot run here).
+static int pair_capacity(int sms) {
+  static int pairs = -1;
+  if (pairs >= 0) return pairs;
+  pairs = 0;
+  const char* e = getenv("MORMOT_B200_PAIR");
+  if (e && e[0] == '0') return pairs;
+  if (cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           TC2_SMEM) != cudaSuccess) {
+    cudaGetLastError();
+    return pairs;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * sms);
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = TC2_SMEM;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return pairs;
+  }
+  pairs = n > sms / 2 ? sms / 2 : n;
+  return pairs;
+}
+MB_EXPORT int mb_gemm_tc_pairs(int sms) { return pair_capacity(sms); }
+
+template <typename... KArgs, typename... Args>
+static cudaError_t mb_launch_pair(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = mb_pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 // C[M, N] = (or +=) the sum over the splits, added in split order
@@ -412,6 +614,46 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     }
     p.kb_per_split = (nkb + p.splits - 1) / p.splits;
     p.splits = (nkb + p.kb_per_split - 1) / p.kb_per_split;
+  }
+  const int pairs = (!swap && N >= TC2_BN && M > 128 &&
+                     (M % 256 == 0 || M % 256 > 128 || M >= 1024))
+                        ? pair_capacity(sms)
+                        : 0;
+  if (pairs > 0) {
+    const int tiles_m = (M + 255) / 256, tiles_n = (N + TC2_BN - 1) / TC2_BN;
+    const int tiles = tiles_m * tiles_n;
+    p.splits = 1;
+    if (workspace && epilogue != TC_SWIGLU && tiles < pairs && nkb >= 8) {
+      int want = (2 * pairs + tiles - 1) / tiles;
+      if (want > nkb / 4) want = nkb / 4;
+      const long long per = (long long)M * N;
+      if (want > workspace_floats / per) want = (int)(workspace_floats / per);
+      if (want > 1) p.splits = want;
+    }
+    p.kb_per_split = (nkb + p.splits - 1) / p.splits;
+    p.splits = (nkb + p.kb_per_split - 1) / p.kb_per_split;
+    CUtensorMap tmA, tmB;
+    if (!mb_make_map_bf16(&tmA, A, M, K, lda, 128, "mb_gemm_tc input")) return -1;
+    if (!mb_make_map_bf16(&tmB, W, N, K, K, 128, "mb_gemm_tc weight")) return -1;
+    const int mode = p.splits > 1 ? TC_PARTIAL : epilogue;
+    float* partial = p.splits > 1 ? workspace : nullptr;
+    const int num_tiles = tiles * p.splits;
+    const int grid = 2 * (num_tiles < pairs ? num_tiles : pairs);
+    mb_launch_pair(gemm_tc_pair_kernel, dim3(grid), dim3(TC_THREADS), TC2_SMEM, s, tmA, tmB, C,
+                   c_dtype, (long long)ldc, M, N, K, p.kb_per_split, mode, partial,
+                   (long long)M * N, (long long)N, tiles_m, tiles_n, num_tiles, error);
+    cudaError_t le = cudaGetLastError();
+    if (le != cudaSuccess) MB_FAIL("mb_gemm_tc (pairs): %s", cudaGetErrorString(le));
+    g_last_launches = (p.splits > 1 && !defer) ? 2 : 1;
+    g_last_splits = p.splits;
+    if (p.splits > 1 && !defer) {
+      const size_t total = (size_t)M * N;
+      const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+      mb_launch(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, s, workspace, p.splits,
+                (long long)M * N, C, c_dtype, (long long)ldc, M, N, epilogue);
+      MB_CHECK_LAUNCH("mb_gemm_tc reduce");
+    }
+    return 0;
   }
   CUtensorMap tmA, tmB;
   if (swap) {
