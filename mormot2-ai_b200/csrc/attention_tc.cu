@@ -5,7 +5,8 @@
 //
 // A CTA takes 128 consecutive new tokens of one sequence and one query head and walks the
 // pages of the cache that these tokens see (64 keys a page):
-//   warp 0      loads Q once, then K and V of page after page into a ring of two stages;
+//   warp 0      loads Q once, then K and V of page after page into rings of two stages each
+//               (K one page ahead of V: its stage is free again after the first product);
 //   warp 1      issues S = Q·Kᵀ (128 x 64), and when P is ready O += P·V (128 x 128);
 //   warps 2-5   read S, mask it (causal bound and window by position), keep the row maximum
 //               and sum, write P = exp2(S - max) as bfloat16 into shared memory for the second
@@ -94,15 +95,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
   const uint32_t sV = sK + AT_STAGES * AT_KV_BYTES;
   const uint32_t sP = sV + AT_STAGES * AT_KV_BYTES;
   const uint32_t bars = sP + AT_P_BYTES;
-  const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = bars + 8 + 8 * AT_STAGES;
-  const uint32_t s_full = kv_empty0 + 8 * AT_STAGES, s_free = s_full + 8, p_full = s_full + 16;
+  const uint32_t q_full = bars, k_full0 = bars + 8, k_empty0 = k_full0 + 8 * AT_STAGES;
+  const uint32_t v_full0 = k_empty0 + 8 * AT_STAGES, v_empty0 = v_full0 + 8 * AT_STAGES;
+  const uint32_t s_full = v_empty0 + 8 * AT_STAGES, s_free = s_full + 8, p_full = s_full + 16;
   const uint32_t o_done = s_full + 24, slot = s_full + 32;
   volatile uint32_t* slot_ptr = (volatile uint32_t*)(at_smem + (slot - raw));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, h = blockIdx.y;
+  // heads fastest (the query heads of one KV head run side by side and share its pages in L2),
+  // and the last row tiles, which see the most pages, first
+  const int b = blockIdx.z, h = blockIdx.x;
   const int start = seq_start[b], n_new = seq_start[b + 1] - start;
-  const int row0 = blockIdx.x * AT_ROWS;
+  const int row0 = (int)(gridDim.y - 1 - blockIdx.y) * AT_ROWS;
   if (row0 >= n_new) return;  // the whole CTA, before anything is set up
   const int past = seq_past[b], slot_of_seq = seq_slot[b];
   const int g = h / (nh / nkv);
@@ -113,8 +117,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < AT_STAGES; ++i) {
-      mbar_init(kv_full0 + 8 * i, 1);
-      mbar_init(kv_empty0 + 8 * i, 1);
+      mbar_init(k_full0 + 8 * i, 1);
+      mbar_init(k_empty0 + 8 * i, 1);
+      mbar_init(v_full0 + 8 * i, 1);
+      mbar_init(v_empty0 + 8 * i, 1);
     }
     mbar_init(s_full, 1);
     mbar_init(s_free, 4);
@@ -139,18 +145,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
       mbar_expect_tx(q_full, AT_Q_BYTES);
       tma_load_2d(sQ, &tmQ, h * AT_HD, start + row0, q_full);
       tma_load_2d(sQ + AT_Q_BYTES / 2, &tmQ, h * AT_HD + 64, start + row0, q_full);
-      for (int j = 0; j < n_pages; ++j) {
-        const int st = j % AT_STAGES;
+      // K of a page is free again after the first product of the page two before, V only after
+      // its second product: K runs one page ahead of V so that neither load waits for the other
+      auto row_of = [&](int j) {
         const int p = page0 + j;
         const int page =
             page_table[(size_t)slot_of_seq * max_pages + (ring_pages > 0 ? p % ring_pages : p)];
-        const int y = (page * nkv + g) * MB_PAGE;
-        mbar_wait(kv_empty0 + 8 * st, ((j / AT_STAGES) & 1) ^ 1, error, 11);
-        mbar_expect_tx(kv_full0 + 8 * st, 2 * AT_KV_BYTES);
-        tma_load_2d(sK + st * AT_KV_BYTES, &tmK, 0, y, kv_full0 + 8 * st);
-        tma_load_2d(sK + st * AT_KV_BYTES + AT_KV_BYTES / 2, &tmK, 64, y, kv_full0 + 8 * st);
-        tma_load_2d(sV + st * AT_KV_BYTES, &tmV, 0, y, kv_full0 + 8 * st);
-        tma_load_2d(sV + st * AT_KV_BYTES + AT_KV_BYTES / 2, &tmV, 64, y, kv_full0 + 8 * st);
+        return (page * nkv + g) * MB_PAGE;
+      };
+      auto load_k = [&](int j) {
+        const int st = j % AT_STAGES, y = row_of(j);
+        mbar_wait(k_empty0 + 8 * st, ((j / AT_STAGES) & 1) ^ 1, error, 11);
+        mbar_expect_tx(k_full0 + 8 * st, AT_KV_BYTES);
+        tma_load_2d(sK + st * AT_KV_BYTES, &tmK, 0, y, k_full0 + 8 * st);
+        tma_load_2d(sK + st * AT_KV_BYTES + AT_KV_BYTES / 2, &tmK, 64, y, k_full0 + 8 * st);
+      };
+      load_k(0);
+      for (int j = 0; j < n_pages; ++j) {
+        if (j + 1 < n_pages) load_k(j + 1);
+        const int st = j % AT_STAGES, y = row_of(j);
+        mbar_wait(v_empty0 + 8 * st, ((j / AT_STAGES) & 1) ^ 1, error, 10);
+        mbar_expect_tx(v_full0 + 8 * st, AT_KV_BYTES);
+        tma_load_2d(sV + st * AT_KV_BYTES, &tmV, 0, y, v_full0 + 8 * st);
+        tma_load_2d(sV + st * AT_KV_BYTES + AT_KV_BYTES / 2, &tmV, 64, y, v_full0 + 8 * st);
       }
     }
   } else if (warp == 1) {
@@ -162,7 +179,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
       // page finds its scores ready and the first product runs under the softmax before it
       auto issue_s = [&](int j) {
         const int st = j % AT_STAGES;
-        mbar_wait(kv_full0 + 8 * st, (j / AT_STAGES) & 1, error, 13);
+        mbar_wait(k_full0 + 8 * st, (j / AT_STAGES) & 1, error, 13);
         if (j > 0) mbar_wait(s_free, (j - 1) & 1, error, 14);  // S of the page before was read
         tc_fence_after_sync();
 #pragma unroll
@@ -172,12 +189,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
               umma_desc_k128(sK + st * AT_KV_BYTES + (k / 4) * (AT_KV_BYTES / 2) + (k % 4) * 32);
           umma_bf16(tS, da, db, idesc_s, k > 0);
         }
+        umma_commit(k_empty0 + 8 * st);  // K of this page has been read
         umma_commit(s_full);
       };
       issue_s(0);
       for (int j = 0; j < n_pages; ++j) {
         const int st = j % AT_STAGES;
         if (j + 1 < n_pages) issue_s(j + 1);
+        mbar_wait(v_full0 + 8 * st, (j / AT_STAGES) & 1, error, 9);
         mbar_wait(p_full, j & 1, error, 15);  // P of this page is in shared memory
         tc_fence_after_sync();
 #pragma unroll
@@ -189,7 +208,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
                 sV + st * AT_KV_BYTES + half * (AT_KV_BYTES / 2) + k * 2048, AT_KV_BYTES / 2);
             umma_bf16(tO + half * 64, da, db, idesc_o, (j | k) != 0);
           }
-        umma_commit(kv_empty0 + 8 * st);  // K and V of this page have been read
+        umma_commit(v_empty0 + 8 * st);  // V of this page has been read
         umma_commit(o_done);
       }
     }
@@ -299,7 +318,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
 // out[t, h, :] for the new tokens of B sequences over the cache, heads of 128 values.
 // q: [T, q_cols] bfloat16 with head h of token t at q + t * q_stride + h * 128 (the fused qkv
 // rows serve); kpool / vpool: [pool_rows, 128] with pool_rows = pages * kv_heads * 64.
-// `error`: a device word that receives 11..18 if a wait in the kernel ran out.
+// `error`: a device word that receives 9..19 if a wait in the kernel ran out.
 MB_EXPORT int mb_attention_prefill_tc(const void* q, int q_stride, int q_cols, void* out,
                                       int out_stride, const void* kpool, const void* vpool,
                                       long long pool_rows, const int* page_table, int max_pages,
@@ -324,7 +343,9 @@ MB_EXPORT int mb_attention_prefill_tc(const void* q, int q_stride, int q_cols, v
     if (e != cudaSuccess) MB_FAIL("mb_attention_prefill_tc: %s", cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((max_new + AT_ROWS - 1) / AT_ROWS, nh, B);
+  const int tiles = (max_new + AT_ROWS - 1) / AT_ROWS;
+  if (tiles > 65535) MB_FAIL("mb_attention_prefill_tc: %d new tokens in one sequence", max_new);
+  dim3 grid(nh, tiles, B);
   mb_launch(attn_prefill_tc_kernel, grid, dim3(AT_THREADS), AT_SMEM, (cudaStream_t)stream, tmQ,
             tmK, tmV, (bf16*)out, out_stride, page_table, max_pages, ring_pages, seq_start,
             seq_past, seq_slot, nh, nkv, window, scale * 1.4426950408889634f, error);
