@@ -303,15 +303,15 @@ __global__ void qk_norm_rope_store_kernel(
 }
 
 
-// The same for bfloat16 heads of 64, 128 or 256 values that rotate as a whole: one warp per
-// (token, head), every lane holds V = hd / 64 neighbouring values of the first half and their
+// The same for bfloat16 heads of 64, 128 or 256 values that rotate as a whole, for steps of few
+// tokens (as many small warps in flight as possible): one warp per (token, head), every lane holds V = hd / 64 neighbouring values of the first half and their
 // rotation partners of the second half, so nothing goes through shared memory. The source is
 // the fused qkv row, or (PARTIAL) the float32 partial sums of a split product
 // [parts][T][width], which are added up here in split order. q goes to q_out [T, nh * hd] when
 // given, else back in place.
 template <int V, typename TW, bool PARTIAL>
 __global__ void __launch_bounds__(QK_WARPS * 32)
-qk_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partial, int parts,
+qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partial, int parts,
                size_t part_stride, __nv_bfloat16* __restrict__ q_out,
                const TW* __restrict__ q_norm, const TW* __restrict__ k_norm, float eps,
                const float* __restrict__ inv_freq, const int* __restrict__ tok_seq,
@@ -392,6 +392,136 @@ qk_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partia
   }
 }
 
+// And for steps of many tokens, with 16-byte accesses: hd / 16 neighbouring lanes share a head, each holds eight neighbouring values of
+// the first half and their rotation partners of the second half, so nothing goes through
+// shared memory and a warp works on 512 / hd heads at once. A warp takes `passes` such groups
+// of heads of its token one after another and forms the sines and cosines once. The source is
+// the fused qkv row, or (PARTIAL) the float32 partial sums of a split product
+// [parts][T][width], which are added up here in split order. q goes to q_out [T, nh * hd] when
+// given, else back in place.
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __bfloat1622float2(h[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+template <int HD, typename TW, bool PARTIAL>
+__global__ void __launch_bounds__(QK_WARPS * 32)
+qk_wide_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partial, int parts,
+               size_t part_stride, __nv_bfloat16* __restrict__ q_out,
+               const TW* __restrict__ q_norm, const TW* __restrict__ k_norm, float eps,
+               const float* __restrict__ inv_freq, const int* __restrict__ tok_seq,
+               const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
+               const int* __restrict__ page_table, int max_pages, int ring_pages,
+               __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int nh,
+               int nkv, int write_kv, int passes) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  constexpr int HALF = HD / 2, L = HALF / 8, HPP = 32 / L;  // lanes a head, heads a pass
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sl = lane % L, hl = lane / L;
+  const int t = blockIdx.x;
+  const int total = nh + 2 * nkv;
+  const int pos = tok_pos[t];
+  const int group0 = (blockIdx.y * (blockDim.x >> 5) + warp) * passes;
+  float cs[8], sn[8];
+  bool have_angles = false;
+  for (int i = 0; i < passes; ++i) {
+    const int head0 = (group0 + i) * HPP;
+    if (head0 >= total) break;  // the whole warp
+    const int head = head0 + hl;
+    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+    const bool live = head < total && (is_q || write_kv);
+    const size_t col = (size_t)head * HD + 8 * sl;
+    float a[8], b[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = b[j] = 0.f;
+    if (live) {
+      if (PARTIAL) {
+        const float* src0 = partial + (size_t)t * total * HD + col;
+#pragma unroll 2
+        for (int p = 0; p < parts; ++p) {
+          const float4* sa = reinterpret_cast<const float4*>(src0 + (size_t)p * part_stride);
+          const float4* sb = reinterpret_cast<const float4*>(src0 + (size_t)p * part_stride + HALF);
+          const float4 a0 = __ldg(sa), a1 = __ldg(sa + 1), b0 = __ldg(sb), b1 = __ldg(sb + 1);
+          a[0] += a0.x; a[1] += a0.y; a[2] += a0.z; a[3] += a0.w;
+          a[4] += a1.x; a[5] += a1.y; a[6] += a1.z; a[7] += a1.w;
+          b[0] += b0.x; b[1] += b0.y; b[2] += b0.z; b[3] += b0.w;
+          b[4] += b1.x; b[5] += b1.y; b[6] += b1.z; b[7] += b1.w;
+        }
+      } else {
+        const __nv_bfloat16* src = qkv + (size_t)t * total * HD + col;
+        unpack8(*reinterpret_cast<const uint4*>(src), a);
+        unpack8(*reinterpret_cast<const uint4*>(src + HALF), b);
+      }
+    }
+    if (head0 < nh + nkv) {  // some head of this pass is a q or k head (uniform over the warp)
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum = fmaf(a[j], a[j], fmaf(b[j], b[j], sum));
+#pragma unroll
+      for (int o = L / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (!have_angles) {
+        // the lanes that hold the same eight columns of different heads share the work: each
+        // forms 8 / HPP of the eight sines and cosines and hands them round
+        constexpr int PER = 8 / HPP;
+        float my_sn[PER], my_cs[PER];
+#pragma unroll
+        for (int r = 0; r < PER; ++r) {
+          const float angle = inv_freq[8 * sl + hl * PER + r] * (float)pos;  // float32 product
+          sincosf(angle, &my_sn[r], &my_cs[r]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          sn[j] = __shfl_sync(0xffffffffu, my_sn[j % PER], (j / PER) * L + sl);
+          cs[j] = __shfl_sync(0xffffffffu, my_cs[j % PER], (j / PER) * L + sl);
+        }
+        have_angles = true;
+      }
+      if (live && (is_q || is_k)) {
+        const TW* w = is_q ? q_norm : k_norm;
+        if (w) {
+          const float inv = 1.0f / sqrtf(sum / (float)HD + eps);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            a[j] = to_f32<TW>(w[8 * sl + j]) * (a[j] * inv);
+            b[j] = to_f32<TW>(w[HALF + 8 * sl + j]) * (b[j] * inv);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float ra = a[j] * cs[j] - b[j] * sn[j], rb = b[j] * cs[j] + a[j] * sn[j];
+          a[j] = ra;
+          b[j] = rb;
+        }
+      }
+    }
+    if (!live) continue;
+    __nv_bfloat16* dst;
+    if (is_q) {
+      dst = q_out ? q_out + (size_t)t * nh * HD + col : qkv + (size_t)t * total * HD + col;
+    } else {
+      const int g = is_k ? head - nh : head - nh - nkv;
+      const size_t row =
+          kv_row(page_table, max_pages, ring_pages, seq_slot[tok_seq[t]], pos, nkv, g);
+      dst = (is_k ? kpool : vpool) + row * HD + 8 * sl;
+    }
+    *reinterpret_cast<uint4*>(dst) = pack8(a);
+    *reinterpret_cast<uint4*>(dst + HALF) = pack8(b);
+  }
+}
+
 // `partial` (may be null): float32 [parts][T][(nh + 2 nkv) hd] partial sums that stand for qkv
 // (bfloat16 heads of 64/128/256 values that rotate as a whole only); `q_out` (may be null):
 // where q goes instead of back into qkv, [T, nh * hd].
@@ -409,19 +539,40 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
   if (hd <= 0 || hd > 1024) MB_FAIL("mb_qk_norm_rope_store: heads of %d", hd);
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(T, (nh + 2 * nkv + QK_WARPS - 1) / QK_WARPS);
-  const bool fast = dtype == MB_BF16 && rot_dim == hd && (hd == 64 || hd == 128 || hd == 256);
+  const bool aligned = !(((uintptr_t)qkv | (uintptr_t)partial | (uintptr_t)q_out |
+                          (uintptr_t)kpool | (uintptr_t)vpool) & 15) && (part_stride & 3) == 0;
+  const bool fast = dtype == MB_BF16 && rot_dim == hd && (hd == 64 || hd == 128 || hd == 256) &&
+                    aligned;
   if ((partial || q_out) && !fast)
     MB_FAIL("mb_qk_norm_rope_store: partial sums or a separate q for heads of %d values "
-            "(%d rotate) are not supported", hd, rot_dim);
+            "(%d rotate)%s are not supported", hd, rot_dim, aligned ? "" : ", not 16-byte aligned,");
   if (fast) {
     typedef __nv_bfloat16 bf;
-#define QKF(V_, TW_, P_)                                                                       \
-  mb_launch(qk_fast_kernel<V_, TW_, P_>, dim3(grid), dim3(QK_WARPS * 32), 0, s,                                    \
+    if (T < 512) {
+#define QKN(V_, TW_, P_)                                                                       \
+  mb_launch(qk_narrow_kernel<V_, TW_, P_>, grid, dim3(QK_WARPS * 32), 0, s,                    \
       (bf*)qkv, partial, parts, (size_t)part_stride, (bf*)q_out, (const TW_*)q_norm,           \
       (const TW_*)k_norm, eps, inv_freq, tok_seq, tok_pos, seq_slot, page_table, max_pages,    \
       ring_pages, (bf*)kpool, (bf*)vpool, nh, nkv, write_kv)
+#define QKN_V(TW_, P_)                                                                         \
+  if (hd == 64) QKN(1, TW_, P_); else if (hd == 128) QKN(2, TW_, P_); else QKN(4, TW_, P_)
+      if (w_dtype == MB_F32) { if (partial) { QKN_V(float, true); } else { QKN_V(float, false); } }
+      else { if (partial) { QKN_V(bf, true); } else { QKN_V(bf, false); } }
+#undef QKN_V
+#undef QKN
+      MB_CHECK_LAUNCH("mb_qk_norm_rope_store");
+    }
+    // groups of 512 / hd heads: blocks of four warps that take three groups each
+    const int groups = ((nh + 2 * nkv) * hd + 511) / 512;
+    const int warps = QK_WARPS, passes = 3;
+    dim3 fgrid(T, (groups + warps * passes - 1) / (warps * passes));
+#define QKF(HD_, TW_, P_)                                                                      \
+  mb_launch(qk_wide_kernel<HD_, TW_, P_>, fgrid, dim3(warps * 32), 0, s,                       \
+      (bf*)qkv, partial, parts, (size_t)part_stride, (bf*)q_out, (const TW_*)q_norm,           \
+      (const TW_*)k_norm, eps, inv_freq, tok_seq, tok_pos, seq_slot, page_table, max_pages,    \
+      ring_pages, (bf*)kpool, (bf*)vpool, nh, nkv, write_kv, passes)
 #define QKF_V(TW_, P_)                                                                         \
-  if (hd == 64) QKF(1, TW_, P_); else if (hd == 128) QKF(2, TW_, P_); else QKF(4, TW_, P_)
+  if (hd == 64) QKF(64, TW_, P_); else if (hd == 128) QKF(128, TW_, P_); else QKF(256, TW_, P_)
     if (w_dtype == MB_F32) { if (partial) { QKF_V(float, true); } else { QKF_V(float, false); } }
     else { if (partial) { QKF_V(bf, true); } else { QKF_V(bf, false); } }
 #undef QKF_V

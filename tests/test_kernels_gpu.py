@@ -324,6 +324,36 @@ def test_qk_norm_rope_store(dtype, nh, nkv, hd, rot):
         assert float(line2.k.float().abs().sum()) == 0
 
 
+def test_qk_norm_rope_store_many_tokens():
+    """With many tokens in a step a warp takes several heads one after another and forms the
+    sines and cosines of its token once: every head of every token, q, k and v, in bfloat16."""
+    nh, nkv, hd, T = 5, 2, 128, 520
+    rng = np.random.default_rng(7)
+    line = make_line(1, 1024, nkv, hd, torch.bfloat16, seed=3)
+    step = make_step([(0, 100, [0] * T, [])])
+    qkv = torch.tensor(rng.standard_normal((T, (nh + 2 * nkv) * hd)),
+                       dtype=torch.float32).to(torch.bfloat16)
+    qn = torch.tensor(1 + 0.1 * rng.standard_normal(hd), dtype=torch.float32)
+    kn = torch.tensor(1 + 0.1 * rng.standard_normal(hd), dtype=torch.float32)
+    inv = plain.inverse_frequencies(1e6, hd)
+    dev = qkv.to(DEV)
+    K.qk_norm_rope_store(dev, qn.to(DEV), kn.to(DEV), 1e-6, torch.tensor(inv).to(DEV), hd, step,
+                         line, nh, nkv, hd, True)
+    src = qkv.float().numpy()
+    got_q = dev[:, :nh * hd].float().cpu().numpy()
+    for t in range(0, T, 7):
+        cos, sin = plain.rotary_tables(inv, [100 + t])
+
+        def normed(x, w, heads):
+            y = plain.rms_norm(x.reshape(heads, hd), w.numpy(), 1e-6)
+            return plain.rope(y.reshape(1, heads * hd), heads, hd, cos, sin).reshape(heads, hd)
+        assert rel(got_q[t].reshape(nh, hd), normed(src[t, :nh * hd], qn, nh)) <= 1.6e-2
+        k_got, v_got = read_line(line, 0, 100 + t)
+        assert rel(k_got.numpy(), normed(src[t, nh * hd:(nh + nkv) * hd], kn, nkv)) <= 1.6e-2
+        assert np.array_equal(v_got.numpy(), src[t, (nh + nkv) * hd:].reshape(nkv, hd))
+    assert int((line.k.float().abs().sum(dim=(1, 3)) > 0).sum()) == T
+
+
 def test_argmax_ties_nan_and_wide_rows():
     nan, inf = float("nan"), float("inf")
     rows = [[1.0, 3.0, 3.0, 2.0], [nan, -inf, nan, -inf], [nan, nan, nan, nan],
