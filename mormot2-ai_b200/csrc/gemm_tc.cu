@@ -290,21 +290,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 // ---------------------------------------------------------------------------- CTA pairs
-// The prefill form for many tokens: two CTAs of a cluster share one tile of 256 tokens x 256
-// output features. Each loads its 128 token rows and its 128 of the 256 weight rows (half the
-// shared-memory traffic of two separate 128 x 256 tiles, so six stages of 32 KB fit instead of
-// four of 48 KB), rank 0 issues tcgen05.mma.cta_group::2 for both, and each CTA's epilogue
+// The prefill form for many tokens: two CTAs of a cluster share one tile of 256 tokens x BN
+// output features (up to 256). Each loads its 128 token rows and its half of the weight rows
+// (half the shared-memory traffic of two separate 128 x 256 tiles, so six stages of 32 KB fit
+// instead of four of 48 KB), rank 0 issues tcgen05.mma.cta_group::2 for both, and each CTA's epilogue
 // warps read the 128 accumulator lanes that landed in its own tensor memory.
 //   full[s]      in rank 0: both CTAs' TMA loads complete their bytes there
 //   empty[s]     in both:   a multicast commit of rank 0's MMA thread frees the stage in both
 //   acc_full[b]  in both:   multicast commit after a tile's last MMA
 //   acc_empty[b] in rank 0: the eight epilogue warps of the pair arrive (rank 1's from afar)
-#define TC2_BN 256
-#define TC2_HALF (128 * TC_BK * 2)  // one CTA's share of either operand in a stage
-#define TC2_STAGES 6
-#define TC2_COLS 256
-#define TC2_SMEM (1024 + TC2_STAGES * 2 * TC2_HALF + 1024)
+// The tile's width BN (a multiple of 16 up to 256) is chosen so that the last round of tiles
+// leaves few pairs idle.
+#define TC2_A_HALF (128 * TC_BK * 2)  // one CTA's 128 token rows of a stage
+#define TC2_COLS 256                  // tensor-memory columns of one accumulator
+template <int BN> struct Tc2Cfg {
+  static constexpr int B_HALF = (BN / 2) * TC_BK * 2;  // one CTA's half of the weight rows
+  static constexpr int STAGE = TC2_A_HALF + B_HALF;
+  static constexpr int STAGES = (200 * 1024) / STAGE > 8 ? 8 : (200 * 1024) / STAGE;
+  static constexpr int SMEM = 1024 + STAGES * STAGE + 1024;
+};
 
+template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     void* __restrict__ C, int c_dtype, long long ldc, int M, int N, int K,
@@ -314,10 +320,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  const uint32_t sA = base, sB = base + TC2_STAGES * TC2_HALF;
-  const uint32_t bars = sB + TC2_STAGES * TC2_HALF;
-  const uint32_t full0 = bars, empty0 = bars + 8 * TC2_STAGES;
-  const uint32_t acc_full0 = bars + 16 * TC2_STAGES, acc_empty0 = acc_full0 + 16;
+  using Cfg = Tc2Cfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  const uint32_t sA = base, sB = base + STAGES * TC2_A_HALF;
+  const uint32_t bars = sB + STAGES * Cfg::B_HALF;
+  const uint32_t full0 = bars, empty0 = bars + 8 * STAGES;
+  const uint32_t acc_full0 = bars + 16 * STAGES, acc_empty0 = acc_full0 + 16;
   const uint32_t slot = acc_empty0 + 16;
   volatile uint32_t* slot_ptr = (volatile uint32_t*)(smem_raw + (slot - raw));
 
@@ -328,7 +336,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int tiles_mn = tiles_m * tiles_n;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < TC2_STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
@@ -355,22 +363,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int w = pair; w < num_tiles; w += pairs) {
         const int rem = w % tiles_mn;
         const int m0 = (rem % tiles_m) * 256 + (int)rank * 128;
-        const int n0 = (rem / tiles_m) * TC2_BN + (int)rank * 128;
+        const int n0 = (rem / tiles_m) * BN + (int)rank * (BN / 2);
         const int kb0 = (w / tiles_mn) * kb_per_split;
         const int nkb = min(kb_per_split, nkb_total - kb0);
         for (int i = 0; i < nkb; ++i) {
           mbar_wait(empty0 + 8 * s, ph ^ 1, error, 11);
-          if (rank == 0) mbar_expect_tx(full0 + 8 * s, 4 * TC2_HALF);
+          if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * Cfg::STAGE);
           const uint32_t full_lead = cluster_addr_of(full0 + 8 * s, 0);
-          tma_load_2d_pair(sA + s * TC2_HALF, &tmA, (kb0 + i) * TC_BK, m0, full_lead);
-          tma_load_2d_pair(sB + s * TC2_HALF, &tmB, (kb0 + i) * TC_BK, n0, full_lead);
-          if (++s == TC2_STAGES) { s = 0; ph ^= 1; }
+          tma_load_2d_pair(sA + s * TC2_A_HALF, &tmA, (kb0 + i) * TC_BK, m0, full_lead);
+          tma_load_2d_pair(sB + s * Cfg::B_HALF, &tmB, (kb0 + i) * TC_BK, n0, full_lead);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     if (rank == 0 && elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_bf16(256, TC2_BN);
+      constexpr uint32_t idesc = umma_idesc_bf16(256, BN);
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
@@ -384,13 +392,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int i = 0; i < nkb; ++i) {
           mbar_wait(full0 + 8 * s, ph, error, 12);
           tc_fence_after_sync();
-          const uint64_t da = umma_desc_k128(sA + s * TC2_HALF);
-          const uint64_t db = umma_desc_k128(sB + s * TC2_HALF);
+          const uint64_t da = umma_desc_k128(sA + s * TC2_A_HALF);
+          const uint64_t db = umma_desc_k128(sB + s * Cfg::B_HALF);
 #pragma unroll
           for (int k = 0; k < TC_BK / 16; ++k)
             umma_bf16_pair(acc, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
           umma_commit_pair(empty0 + 8 * s, 3);
-          if (++s == TC2_STAGES) { s = 0; ph ^= 1; }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         umma_commit_pair(acc_full0 + 8 * b, 3);
       }
@@ -401,7 +409,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int it = 0;
     for (int w = pair; w < num_tiles; w += pairs, ++it) {
       const int rem = w % tiles_mn, z = w / tiles_mn;
-      const int n0 = (rem / tiles_m) * TC2_BN;
+      const int n0 = (rem / tiles_m) * BN;
       const int a = (rem % tiles_m) * 256 + (int)rank * 128 + lane_row;
       const int b = it & 1;
       mbar_wait(acc_full0 + 8 * b, (it >> 1) & 1, error, 13);
@@ -409,7 +417,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t taddr = tmem + b * TC2_COLS + ((uint32_t)(q * 32) << 16);
       float* part = partial ? partial + z * partial_stride : nullptr;
 #pragma unroll 1
-      for (int c0 = 0; c0 < TC2_BN; c0 += 16) {
+      for (int c0 = 0; c0 < BN; c0 += 16) {
         if (n0 + c0 >= N) break;
         float v[16];
         tmem_ld16(taddr + c0, v);
@@ -437,15 +445,15 @@ static int pair_capacity(int sms) {
   pairs = 0;
   const char* e = getenv("MORMOT_B200_PAIR");
   if (e && e[0] == '0') return pairs;
-  if (cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           TC2_SMEM) != cudaSuccess) {
+  if (cudaFuncSetAttribute(gemm_tc_pair_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           Tc2Cfg<256>::SMEM) != cudaSuccess) {
     cudaGetLastError();
     return pairs;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * sms);
   cfg.blockDim = dim3(TC_THREADS);
-  cfg.dynamicSmemBytes = TC2_SMEM;
+  cfg.dynamicSmemBytes = Tc2Cfg<256>::SMEM;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
@@ -454,7 +462,7 @@ static int pair_capacity(int sms) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<256>, &cfg) != cudaSuccess) {
     cudaGetLastError();
     return pairs;
   }
@@ -481,6 +489,52 @@ static cudaError_t mb_launch_pair(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
   cfg.attrs = attr;
   cfg.numAttrs = mb_pdl_enabled() ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+template <int BN>
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int c_dtype,
+                       long long ldc, int M, int N, int K, int kb_per_split, int mode,
+                       float* partial, int tiles_m, int tiles_n, int splits, int pairs,
+                       int* error, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Tc2Cfg<BN>::SMEM);
+    if (e != cudaSuccess) MB_FAIL("mb_gemm_tc (pairs): shared memory of %d bytes: %s",
+                                  Tc2Cfg<BN>::SMEM, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int num_tiles = tiles_m * tiles_n * splits;
+  const int grid = 2 * (num_tiles < pairs ? num_tiles : pairs);
+  mb_launch_pair(gemm_tc_pair_kernel<BN>, dim3(grid), dim3(TC_THREADS), Tc2Cfg<BN>::SMEM, s, tmA,
+                 tmB, C, c_dtype, ldc, M, N, K, kb_per_split, mode, partial, (long long)M * N,
+                 (long long)N, tiles_m, tiles_n, num_tiles, error);
+  cudaError_t le = cudaGetLastError();
+  if (le != cudaSuccess) MB_FAIL("mb_gemm_tc (pairs): %s", cudaGetErrorString(le));
+  return 0;
+}
+
+// The tile width for N output features and tiles_m row tiles on `pairs` CTA pairs: the one
+// whose rounds of tiles take the least time (measured: a full round of tiles of width w takes
+// about w + 40 in units of 0.09 microseconds at K = 4096).
+static int pair_tile_width(int N, int tiles_m, int pairs) {
+  static int forced = -1;  // MORMOT_B200_PAIR_WIDTH: one width for every product (measurements)
+  if (forced < 0) {
+    const char* e = getenv("MORMOT_B200_PAIR_WIDTH");
+    forced = e ? atoi(e) : 0;
+    if (forced < 128 || forced > 256 || forced % 16) forced = 0;
+  }
+  if (forced) return forced;
+  int best = 256;
+  long long best_cost = -1;
+  for (int w = 256; w >= 128; w -= 16) {
+    const long long tiles = (long long)tiles_m * ((N + w - 1) / w);
+    const long long rounds = (tiles + pairs - 1) / pairs;
+    const long long cost = rounds * (w + 40);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = w; }
+  }
+  return best;
 }
 
 // C[M, N] = (or +=) the sum over the splits, added in split order
@@ -615,12 +669,14 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     p.kb_per_split = (nkb + p.splits - 1) / p.splits;
     p.splits = (nkb + p.kb_per_split - 1) / p.kb_per_split;
   }
-  const int pairs = (!swap && N >= TC2_BN && M > 128 &&
+  const int pairs = (!swap && N >= 256 && M > 128 &&
                      (M % 256 == 0 || M % 256 > 128 || M >= 1024))
                         ? pair_capacity(sms)
                         : 0;
   if (pairs > 0) {
-    const int tiles_m = (M + 255) / 256, tiles_n = (N + TC2_BN - 1) / TC2_BN;
+    const int tiles_m = (M + 255) / 256;
+    const int bn = pair_tile_width(N, tiles_m, pairs);
+    const int tiles_n = (N + bn - 1) / bn;
     const int tiles = tiles_m * tiles_n;
     p.splits = 1;
     if (workspace && epilogue != TC_SWIGLU && tiles < pairs && nkb >= 8) {
@@ -634,16 +690,22 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     p.splits = (nkb + p.kb_per_split - 1) / p.kb_per_split;
     CUtensorMap tmA, tmB;
     if (!mb_make_map_bf16(&tmA, A, M, K, lda, 128, "mb_gemm_tc input")) return -1;
-    if (!mb_make_map_bf16(&tmB, W, N, K, K, 128, "mb_gemm_tc weight")) return -1;
+    if (!mb_make_map_bf16(&tmB, W, N, K, K, bn / 2, "mb_gemm_tc weight")) return -1;
     const int mode = p.splits > 1 ? TC_PARTIAL : epilogue;
     float* partial = p.splits > 1 ? workspace : nullptr;
-    const int num_tiles = tiles * p.splits;
-    const int grid = 2 * (num_tiles < pairs ? num_tiles : pairs);
-    mb_launch_pair(gemm_tc_pair_kernel, dim3(grid), dim3(TC_THREADS), TC2_SMEM, s, tmA, tmB, C,
-                   c_dtype, (long long)ldc, M, N, K, p.kb_per_split, mode, partial,
-                   (long long)M * N, (long long)N, tiles_m, tiles_n, num_tiles, error);
-    cudaError_t le = cudaGetLastError();
-    if (le != cudaSuccess) MB_FAIL("mb_gemm_tc (pairs): %s", cudaGetErrorString(le));
+    int rc = 0;
+    switch (bn) {
+#define PAIR(W_)                                                                                \
+  case W_:                                                                                      \
+    rc = launch_pair<W_>(tmA, tmB, C, c_dtype, (long long)ldc, M, N, K, p.kb_per_split, mode,   \
+                         partial, tiles_m, tiles_n, p.splits, pairs, error, s);                 \
+    break
+      PAIR(256); PAIR(240); PAIR(224); PAIR(208); PAIR(192); PAIR(176); PAIR(160); PAIR(144);
+      PAIR(128);
+#undef PAIR
+      default: MB_FAIL("mb_gemm_tc (pairs): tile width %d", bn);
+    }
+    if (rc) return rc;
     g_last_launches = (p.splits > 1 && !defer) ? 2 : 1;
     g_last_splits = p.splits;
     if (p.splits > 1 && !defer) {

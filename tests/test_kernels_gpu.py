@@ -112,11 +112,12 @@ def test_gemm_simt(M, N, Kd, a_dt, w_dt, c_dt):
                                     (64, 1000, 1024), (65, 77, 72), (128, 384, 192),
                                     (300, 509, 320), (1030, 264, 520), (9, 4096, 2048),
                                     (8, 19000, 256), (40, 40000, 128), (3, 150, 64),
-                                    (448, 778, 200), (512, 512, 2048), (256, 256, 64)])
+                                    (448, 778, 200), (512, 512, 2048), (256, 256, 64),
+                                    (2048, 4096, 64), (1024, 6144, 72), (2048, 2304, 64)])
 def test_gemm_tensor_cores(rt, M, N, Kd):
     """The forms of csrc/gemm_tc.cu (weight rows on the TMEM lanes for few tokens, tokens on the
-    lanes of one CTA, 256 tokens on the lanes of a CTA pair), tails in every dimension, the split
-    of K, all epilogues."""
+    lanes of one CTA, 256 tokens on the lanes of a CTA pair with its tile widths), tails in every
+    dimension, the split of K, all epilogues."""
     g = torch.Generator().manual_seed(M + N + Kd)
     a = torch.randn(M, Kd, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, Kd, generator=g) * 0.1).to(torch.bfloat16)
