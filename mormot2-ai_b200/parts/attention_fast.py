@@ -10,20 +10,22 @@ from .. import kernels as K
 from ..cache.pages import pages_for
 
 FAST_HEAD_DIMS = (64, 128)
+MAX_DECODE_SPLITS = 16
 
 
 def decode_splits(line, T: int, nh: int, nkv: int, sms: int, window: int) -> int:
     """Over how many CTAs the pages of a sequence are dealt out in a decode step of T tokens.
     Every CTA pays a fixed price (index loads before its first key, the merge at its end), so
-    few, long CTAs win: as many as give one round of two CTAs per SM, and no more than the most
-    pages that a sequence can hold in this line (the lengths of the moment do not count: a
-    captured launch must stay valid as sequences grow)."""
+    few, long CTAs win: as many as give one round of two CTAs per SM, at most 16 (beyond that the
+    merge of the partial results costs more than the shorter CTAs save: measured at batch 1),
+    and no more than the most pages that a sequence can hold in this line (the lengths of the
+    moment do not count: a captured launch must stay valid as sequences grow)."""
     pages = line.max_pages
     if window > 0:
         pages = min(pages, pages_for(window) + 1)
     subs = (nh // nkv + 15) // 16
     groups = max(1, T * nkv * subs)
-    return max(1, min((2 * sms) // groups, pages))
+    return max(1, min((2 * sms) // groups, pages, MAX_DECODE_SPLITS))
 
 
 def run(rt, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> bool:
