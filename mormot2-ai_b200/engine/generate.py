@@ -139,9 +139,15 @@ class EngineStepper:
         else:
             ctx_slots = self._torch.tensor([slot for slot, _ in entries],
                                            dtype=self._torch.int32, device=logits.device)
-        tokens = self.sampler.pick(logits, ctx_slots, self.sampling, self.vocab_limit)
-        host = tokens.cpu()
-        self.engine.rt.check_cheap()
+        rt = self.engine.rt
+        rows = logits.shape[0]
+        box = rt.token_box(rows)
+        tokens = self.sampler.pick(logits, ctx_slots, self.sampling, self.vocab_limit, out=box)
         self.h2d_bytes += self.engine.last_h2d_bytes
-        self.d2h_bytes += host.numel() * 4
-        return host.tolist()
+        if box is None:
+            host = tokens.cpu()
+            rt.check_cheap()
+            self.d2h_bytes += host.numel() * 4
+            return host.tolist()
+        self.d2h_bytes += (rows + 1) * 4
+        return rt.read_tokens(rows)

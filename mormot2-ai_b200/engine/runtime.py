@@ -2,10 +2,14 @@
 type (bfloat16, or float32 on the true 32-bit path) and which kernels are allowed."""
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from .. import kernels as K
 from ..errors import KernelError
+
+MAILBOX_TOKENS = 4096
 
 
 class Runtime:
@@ -26,15 +30,36 @@ class Runtime:
         # the partial sums of a split product that its consumer adds up (parts/linear.py)
         self.pending_buf = (torch.empty(8 << 20, dtype=torch.float32, device=self.device)
                             if self.fast_kernels else None)
-        self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # word 0: set by a kernel when one of its bounded waits ran out; the words after it: the
+        # tokens that the sampler chose in a step, so that one copy brings both to the host
+        self.mailbox = torch.zeros(1 + MAILBOX_TOKENS, dtype=torch.int32, device=self.device)
+        self.error_word = self.mailbox[:1]
+        self.host_mailbox = torch.zeros(1 + MAILBOX_TOKENS, dtype=torch.int32).pin_memory()
+        self.mail_event = torch.cuda.Event()
 
     def check(self) -> None:
         """Raises if a kernel recorded that one of its waits ran out (synchronizes)."""
-        code = int(self.error_word.item())
+        self._raise_if(int(self.error_word.item()))
+
+    def _raise_if(self, code: int) -> None:
         if code:
             self.error_word.zero_()
             raise KernelError(f"a kernel gave up a wait (code {code}: 1 load, 2 MMA, "
-                              "3 epilogue); its result is not valid")
+                              "3 epilogue; 4-5, 9-19 attention); its result is not valid")
+
+    def token_box(self, rows: int) -> Optional[torch.Tensor]:
+        """Where a sampler may leave ``rows`` chosen tokens for ``read_tokens`` (None: too many)."""
+        return self.mailbox[1:1 + rows] if rows <= MAILBOX_TOKENS else None
+
+    def read_tokens(self, rows: int) -> list:
+        """The tokens in the token box and the kernels' error word in one copy through pinned
+        memory (waits for the stream); raises like ``check``."""
+        self.host_mailbox[:1 + rows].copy_(self.mailbox[:1 + rows], non_blocking=True)
+        self.mail_event.record()
+        self.mail_event.synchronize()
+        got = self.host_mailbox[:1 + rows].tolist()
+        self._raise_if(got[0])
+        return got[1:]
 
     def check_cheap(self) -> None:
         """Like ``check`` for a caller that has just synchronized anyway."""

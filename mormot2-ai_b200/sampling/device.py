@@ -28,15 +28,18 @@ class DeviceSampler:
         self.states[slot] = s - (1 << 64) if s >= 1 << 63 else s
 
     def pick(self, logits: torch.Tensor, slots: torch.Tensor, sampling: Sampling,
-             vocab_limit: Optional[int] = None) -> torch.Tensor:
+             vocab_limit: Optional[int] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One token per row of ``logits`` [rows, vocab]; ``slots`` int32 [rows] on the device
         names each row's stream. ``vocab_limit``: only the ids below it are candidates (rows of
         a padded embedding that no tokenizer id stands for are never drawn,
-        ``llm.native.pas:2159-2162`` of the reference)."""
+        ``llm.native.pas:2159-2162`` of the reference). ``out``: int32 [rows] on the device to
+        write into (else a new tensor)."""
         rows = logits.shape[0]
         if vocab_limit is not None and vocab_limit < logits.shape[1]:
             logits = logits[:, :vocab_limit]
-        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        if out is None:
+            out = torch.empty(rows, dtype=torch.int32, device=logits.device)
         if sampling.greedy:
             K.argmax(logits, out, self.argmax_scratch if rows <= self.max_slots else None)
         elif not sampling.filtered:
