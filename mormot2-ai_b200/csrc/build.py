@@ -34,6 +34,7 @@ NVCC_FLAGS += os.environ.get("MORMOT_B200_NVCC_FLAGS", "").split()
 # library name -> source file; headers that every library depends on
 SOURCES = {
     "elementwise": "elementwise.cu",
+    "rope": "rope.cu",
     "gemm_simt": "gemm_simt.cu",
     "attention_simt": "attention_simt.cu",
     "sampling": "sampling.cu",

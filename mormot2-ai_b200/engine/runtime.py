@@ -67,7 +67,7 @@ class Runtime:
 
     def libraries(self):
         """The kernel libraries that a model of this runtime needs."""
-        libs = ["elementwise", "gemm_simt", "attention_simt", "sampling"]
+        libs = ["elementwise", "rope", "gemm_simt", "attention_simt", "sampling"]
         if self.fast_kernels:
             libs += ["gemm_tc", "attention_mma", "attention_tc"]
         return libs

@@ -150,7 +150,7 @@ def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, 
     if (q_norm is None) != (k_norm is None):
         raise KernelError("q_norm and k_norm come together")
     wd = code_of(q_norm.dtype) if q_norm is not None else F32
-    _call("elementwise", "mb_qk_norm_rope_store",
+    _call("rope", "mb_qk_norm_rope_store",
           [_vp, _vp, _i, _ll, _vp, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _vp, _vp, _i, _i,
            _vp, _vp, _i, _i, _i, _i, _i, _vp],
           _ptr(qkv), _ptr(partial), partial.shape[0] if partial is not None else 0,

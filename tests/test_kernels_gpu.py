@@ -56,6 +56,24 @@ def test_rmsnorm(H, out_dtype):
     assert rel(out.float().cpu(), want) <= (2e-6 if out_dtype == "float32" else 8e-3)
 
 
+@pytest.mark.parametrize("H", [1000, 2048, 4096, 5128, 16384, 20000])
+def test_rmsnorm_many_rows(H):
+    """More rows than a decode step has: the variants with 256 threads a row, the wide rows
+    that go to 1024 threads, and a row beyond the vector kernels; with partial sums too."""
+    g = torch.Generator().manual_seed(H)
+    x = torch.randn(300, H, generator=g) * 3
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    parts = torch.randn(2, 300, H, generator=g)
+    out = torch.empty(300, H, dtype=torch.bfloat16, device=DEV)
+    K.rmsnorm(x.to(DEV), w.to(DEV), 1e-6, out)
+    assert rel(out.float().cpu(), plain.rms_norm(x.numpy(), w.float().numpy(), 1e-6)) <= 8e-3
+    xd = x.to(DEV)
+    K.rmsnorm(xd, w.to(DEV), 1e-6, out, partial=parts.to(DEV))
+    total = (x + parts[0]) + parts[1]
+    assert torch.equal(xd.cpu(), total)
+    assert rel(out.float().cpu(), plain.rms_norm(total.numpy(), w.float().numpy(), 1e-6)) <= 8e-3
+
+
 def test_rmsnorm_adds_split_partials():
     g = torch.Generator().manual_seed(1)
     x = torch.randn(5, 320, generator=g)
