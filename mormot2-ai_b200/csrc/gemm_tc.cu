@@ -2,17 +2,20 @@
 // operand tiles brought to shared memory by TMA (128-byte swizzle), tcgen05.mma issued by one
 // thread with the float32 accumulator in tensor memory, tcgen05.ld for the epilogue.
 //
-// One kernel serves prefill and decode. The operand on the MMA's M side fills the 128 TMEM
-// lanes of a tile, the other one its columns (16 to 256):
-//   many tokens (prefill):  tokens on the lanes, output features on the columns;
-//   few tokens (decode):    the WEIGHT rows on the lanes and the tokens on the columns, so that
-//                           a step streams each weight byte once through full-width MMAs,
-//                           whatever the batch; the tile is written back transposed.
+// The operand on the MMA's M side fills the TMEM lanes of a tile, the other one its columns
+// (16 to 256). Three forms:
+//   many tokens (prefill):   tokens on the lanes of a PAIR of CTAs (256 of them), output
+//                            features on the columns: gemm_tc_pair_kernel, further down;
+//   65 to 128 tokens:        tokens on the 128 lanes of one CTA, features on the columns;
+//   few tokens (decode):     the WEIGHT rows on the lanes and the tokens on the columns, so that
+//                            a step streams each weight byte once through full-width MMAs,
+//                            whatever the batch; the tile is written back transposed.
 // In the decode form two CTAs share an SM; a weight with few 128-row tiles has its K range
 // split over as many CTAs as fill those places, one with a few more gets tiles of fewer rows so
-// that one round of CTAs covers it evenly. In the prefill form K is split when there are fewer
-// tiles than SMs. Partial sums go to a float32 workspace that the caller provides and are
-// added up in split order by a second kernel (deterministic, no atomics).
+// that one round of CTAs covers it evenly. In the other forms K is split when there are fewer
+// tiles than places. Partial sums go to a float32 workspace that the caller provides and are
+// added up in split order by a second kernel (deterministic, no atomics) or by the caller's
+// next kernel.
 //
 // Epilogues: store (bfloat16 or float32), add into the float32 residual, and SwiGLU for a
 // weight whose rows alternate gate, up, gate, up ...: out[:, i] = silu(y[:, 2i]) * y[:, 2i+1].
