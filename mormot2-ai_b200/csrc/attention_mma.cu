@@ -111,8 +111,8 @@ template <int HD>
 __global__ void __launch_bounds__((DEC_WARPS + 1) * 32, 2)
 attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kpool,
                    const bf16* __restrict__ vpool, const int* __restrict__ page_table,
-                   int max_pages, int ring_pages, const int* __restrict__ tok_seq,
-                   const int* __restrict__ tok_pos, const int* __restrict__ seq_slot, int nh,
+                   int max_pages, int ring_pages, const int* __restrict__ tok_slot,
+                   const int* __restrict__ tok_pos, int nh,
                    int nkv, int window, float scale_log2, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int* __restrict__ error) {
   constexpr int CH = HD / 32;  // 32-dim chunks of q·k
@@ -134,7 +134,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   const int r = lane >> 2, c = lane & 3;
 
   const int pos = tok_pos[t];
-  const int slot = seq_slot[tok_seq[t]];
+  const int slot = tok_slot[t];
   const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
   const int p_first = lo / MB_PAGE + s, p_last = pos / MB_PAGE;
   const int n_pages = p_first <= p_last ? (p_last - p_first) / S + 1 : 0;  // p_first + i * S
@@ -366,8 +366,8 @@ MB_EXPORT long long mb_attention_decode_scratch(int T, int nh, int hd, int split
 // a device word that receives 4 or 5 if a wait of the kernel's copy pipeline ran out.
 MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int out_stride,
                                   const void* kpool, const void* vpool, const int* page_table,
-                                  int max_pages, int ring_pages, const int* tok_seq,
-                                  const int* tok_pos, const int* seq_slot, int T, int nh, int nkv,
+                                  int max_pages, int ring_pages, const int* tok_slot,
+                                  const int* tok_pos, int T, int nh, int nkv,
                                   int hd, int window, float scale, int splits, float* scratch,
                                   long long scratch_floats, int* error, void* stream) {
   if (T <= 0) return 0;
@@ -401,7 +401,7 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
     }                                                                                          \
     mb_launch(attn_decode_kernel<HD_>, grid, dim3((DEC_WARPS + 1) * 32), smem, s,              \
               (const bf16*)q, q_stride, (const bf16*)kpool, (const bf16*)vpool, page_table,    \
-              max_pages, ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, window, scale_log2,  \
+              max_pages, ring_pages, tok_slot, tok_pos, nh, nkv, window, scale_log2,           \
               part_o, part_ml, error);                                                         \
     mb_launch(attn_merge_kernel<HD_>, mgrid, dim3(HD_), 0, s, (const float*)part_o,            \
               (const float*)part_ml, splits, (bf16*)out, out_stride, nh);                      \
@@ -696,8 +696,8 @@ static float* g_static_scratch_ptr[MB_MAX_DEVICES];  // device address per devic
 MB_EXPORT int mb_attention_decode_static(const void* q, int q_stride, void* out, int out_stride,
                                          const void* kpool, const void* vpool,
                                          const int* page_table, int max_pages, int ring_pages,
-                                         const int* tok_seq, const int* tok_pos,
-                                         const int* seq_slot, int T, int nh, int nkv, int hd,
+                                         const int* tok_slot, const int* tok_pos,
+                                         int T, int nh, int nkv, int hd,
                                          int window, float scale, int splits, int* error,
                                          void* stream) {
   if (T <= 0) return 0;
@@ -723,7 +723,7 @@ MB_EXPORT int mb_attention_decode_static(const void* q, int q_stride, void* out,
     g_static_scratch_ptr[device] = p;
   }
   return mb_attention_decode(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
-                             ring_pages, tok_seq, tok_pos, seq_slot, T, nh, nkv, hd, window,
+                             ring_pages, tok_slot, tok_pos, T, nh, nkv, hd, window,
                              scale, splits, g_static_scratch_ptr[device],
                              MB_ATTENTION_DECODE_STATIC_FLOATS, error, stream);
 }

@@ -50,8 +50,8 @@ extern "C" {
  * Returns 0 after the launch, -1 on refusal. */
 int mb_attention_decode_static(const void* q, int q_stride, void* out, int out_stride,
                                const void* kpool, const void* vpool, const int* page_table,
-                               int max_pages, int ring_pages, const int* tok_seq,
-                               const int* tok_pos, const int* seq_slot, int T, int nh, int nkv,
+                               int max_pages, int ring_pages, const int* tok_slot,
+                               const int* tok_pos, int T, int nh, int nkv,
                                int hd, int window, float scale, int splits, int* error,
                                void* stream);
 

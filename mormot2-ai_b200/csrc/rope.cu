@@ -22,8 +22,8 @@ __device__ __forceinline__ float norm_w(const void* w, int w_bf16, int i) {
 template <typename T, typename TW>
 __global__ void qk_norm_rope_store_kernel(
     T* __restrict__ qkv, const TW* __restrict__ q_norm, const TW* __restrict__ k_norm, float eps,
-    const float* __restrict__ inv_freq, int rot_dim, const int* __restrict__ tok_seq,
-    const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
+    const float* __restrict__ inv_freq, int rot_dim, const int* __restrict__ tok_slot,
+    const int* __restrict__ tok_pos,
     const int* __restrict__ page_table, int max_pages, int ring_pages, T* __restrict__ kpool,
     T* __restrict__ vpool, int nh, int nkv, int hd, int write_kv) {
   mb_grid_wait();
@@ -42,7 +42,7 @@ __global__ void qk_norm_rope_store_kernel(
   T* dst = src;
   if (!is_q) {
     const int g = is_k ? head - nh : head - nh - nkv;
-    const size_t row = kv_row(page_table, max_pages, ring_pages, seq_slot[tok_seq[t]], pos, nkv, g);
+    const size_t row = kv_row(page_table, max_pages, ring_pages, tok_slot[t], pos, nkv, g);
     dst = (is_k ? kpool : vpool) + row * hd;
     if (!is_k) {  // values are stored as they are
       for (int i = lane; i < hd; i += 32) dst[i] = src[i];
@@ -88,8 +88,8 @@ qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ part
                size_t part_stride, __nv_bfloat16* __restrict__ q_out,
                const void* __restrict__ q_norm, const void* __restrict__ k_norm, int w_bf16,
                float eps,
-               const float* __restrict__ inv_freq, const int* __restrict__ tok_seq,
-               const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
+               const float* __restrict__ inv_freq, const int* __restrict__ tok_slot,
+               const int* __restrict__ tok_pos,
                const int* __restrict__ page_table, int max_pages, int ring_pages,
                __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int nh,
                int nkv, int write_kv) {
@@ -132,7 +132,7 @@ qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ part
     dst = q_out ? q_out + (size_t)t * nh * HD + col : qkv + (size_t)t * total * HD + col;
   } else {
     const int g = is_k ? head - nh : head - nh - nkv;
-    const size_t row = kv_row(page_table, max_pages, ring_pages, seq_slot[tok_seq[t]], pos, nkv, g);
+    const size_t row = kv_row(page_table, max_pages, ring_pages, tok_slot[t], pos, nkv, g);
     dst = (is_k ? kpool : vpool) + row * HD + V * lane;
   }
   if (is_q || is_k) {
@@ -196,8 +196,8 @@ qk_wide_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partia
                size_t part_stride, __nv_bfloat16* __restrict__ q_out,
                const void* __restrict__ q_norm, const void* __restrict__ k_norm, int w_bf16,
                float eps,
-               const float* __restrict__ inv_freq, const int* __restrict__ tok_seq,
-               const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
+               const float* __restrict__ inv_freq, const int* __restrict__ tok_slot,
+               const int* __restrict__ tok_pos,
                const int* __restrict__ page_table, int max_pages, int ring_pages,
                __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int nh,
                int nkv, int write_kv, int passes) {
@@ -289,7 +289,7 @@ qk_wide_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partia
     } else {
       const int g = is_k ? head - nh : head - nh - nkv;
       const size_t row =
-          kv_row(page_table, max_pages, ring_pages, seq_slot[tok_seq[t]], pos, nkv, g);
+          kv_row(page_table, max_pages, ring_pages, tok_slot[t], pos, nkv, g);
       dst = (is_k ? kpool : vpool) + row * HD + 8 * sl;
     }
     *reinterpret_cast<uint4*>(dst) = pack8(a);
@@ -304,7 +304,7 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
                                     long long part_stride, void* q_out, int dtype,
                                     const void* q_norm, const void* k_norm,
                                     int w_dtype, float eps, const float* inv_freq, int rot_dim,
-                                    const int* tok_seq, const int* tok_pos, const int* seq_slot,
+                                    const int* tok_slot, const int* tok_pos,
                                     const int* page_table, int max_pages, int ring_pages,
                                     void* kpool, void* vpool, int T, int nh, int nkv, int hd,
                                     int write_kv, void* stream) {
@@ -327,8 +327,8 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
     if (T < 512) {
 #define QKN(V_, P_)                                                                            \
   mb_launch(qk_narrow_kernel<V_, P_>, grid, dim3(QK_WARPS * 32), 0, s, (bf*)qkv, partial,      \
-      parts, (size_t)part_stride, (bf*)q_out, q_norm, k_norm, w_bf16, eps, inv_freq, tok_seq,  \
-      tok_pos, seq_slot, page_table, max_pages, ring_pages, (bf*)kpool, (bf*)vpool, nh, nkv,   \
+      parts, (size_t)part_stride, (bf*)q_out, q_norm, k_norm, w_bf16, eps, inv_freq, tok_slot, \
+      tok_pos, page_table, max_pages, ring_pages, (bf*)kpool, (bf*)vpool, nh, nkv,   \
       write_kv)
 #define QKN_V(P_)                                                                              \
   if (hd == 64) QKN(1, P_); else if (hd == 128) QKN(2, P_); else QKN(4, P_)
@@ -343,8 +343,8 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
     dim3 fgrid(T, (groups + warps * passes - 1) / (warps * passes));
 #define QKF(HD_, P_)                                                                           \
   mb_launch(qk_wide_kernel<HD_, P_>, fgrid, dim3(warps * 32), 0, s, (bf*)qkv, partial, parts,  \
-      (size_t)part_stride, (bf*)q_out, q_norm, k_norm, w_bf16, eps, inv_freq, tok_seq,         \
-      tok_pos, seq_slot, page_table, max_pages, ring_pages, (bf*)kpool, (bf*)vpool, nh, nkv,   \
+      (size_t)part_stride, (bf*)q_out, q_norm, k_norm, w_bf16, eps, inv_freq, tok_slot,        \
+      tok_pos, page_table, max_pages, ring_pages, (bf*)kpool, (bf*)vpool, nh, nkv,   \
       write_kv, passes)
 #define QKF_V(P_)                                                                              \
   if (hd == 64) QKF(64, P_); else if (hd == 128) QKF(128, P_); else QKF(256, P_)
@@ -356,8 +356,8 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
   const size_t smem = (size_t)QK_WARPS * hd * sizeof(float);
 #define QK_LAUNCH(T_, TW_)                                                                     \
   mb_launch(qk_norm_rope_store_kernel<T_, TW_>, dim3(grid), dim3(QK_WARPS * 32), smem, s,                         \
-      (T_*)qkv, (const TW_*)q_norm, (const TW_*)k_norm, eps, inv_freq, rot_dim, tok_seq,       \
-      tok_pos, seq_slot, page_table, max_pages, ring_pages, (T_*)kpool, (T_*)vpool, nh, nkv,   \
+      (T_*)qkv, (const TW_*)q_norm, (const TW_*)k_norm, eps, inv_freq, rot_dim, tok_slot,      \
+      tok_pos, page_table, max_pages, ring_pages, (T_*)kpool, (T_*)vpool, nh, nkv,   \
       hd, write_kv)
   if (dtype == MB_F32 && w_dtype == MB_F32) QK_LAUNCH(float, float);
   else if (dtype == MB_F32) QK_LAUNCH(float, __nv_bfloat16);

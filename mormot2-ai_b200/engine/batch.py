@@ -20,6 +20,7 @@ class StepContext:
     tok_ids: torch.Tensor       # int32 [T]
     tok_seq: torch.Tensor       # int32 [T] index of the token's sequence in this pass
     tok_pos: torch.Tensor       # int32 [T] absolute position
+    tok_slot: torch.Tensor      # int32 [T] the cache slot of the token's sequence
     seq_slot: torch.Tensor      # int32 [B]
     seq_start: torch.Tensor     # int32 [B + 1] first packed row of each sequence
     seq_past: torch.Tensor      # int32 [B] positions held before this pass
@@ -39,7 +40,7 @@ class StepBuffers:
 
     def __init__(self, max_tokens: int, max_seqs: int, device: torch.device):
         self.max_tokens, self.max_seqs = max_tokens, max_seqs
-        self.size = 4 * max_tokens + 3 * max_seqs + 1
+        self.size = 5 * max_tokens + 3 * max_seqs + 1
         self.host = torch.zeros(self.size, dtype=torch.int32).pin_memory()
         self.dev = torch.zeros(self.size, dtype=torch.int32, device=device)
         self.copied = torch.cuda.Event()
@@ -54,11 +55,12 @@ class StepBuffers:
         if self.in_flight:
             self.copied.synchronize()  # the last copy must have read the host buffer
         h = self.host
-        o_ids, o_seq, o_pos = 0, T, 2 * T
-        o_slot, o_start, o_past, o_want = 3 * T, 3 * T + B, 3 * T + 2 * B + 1, 3 * T + 3 * B + 1
+        o_ids, o_seq, o_pos, o_tslot = 0, T, 2 * T, 3 * T
+        o_slot, o_start, o_past, o_want = 4 * T, 4 * T + B, 4 * T + 2 * B + 1, 4 * T + 3 * B + 1
         ids: List[int] = []
         seq: List[int] = []
         pos: List[int] = []
+        tslot: List[int] = []
         starts = [0]
         wants: List[int] = []
         for b, (slot, past, tokens, want) in enumerate(seqs):
@@ -66,9 +68,11 @@ class StepBuffers:
             ids.extend(tokens)
             seq.extend([b] * n)
             pos.extend(range(past, past + n))
+            tslot.extend([slot] * n)
             wants.extend(starts[-1] + w for w in want)
             starts.append(starts[-1] + n)
-        flat = (ids + seq + pos + [s[0] for s in seqs] + starts + [s[1] for s in seqs] + wants)
+        flat = (ids + seq + pos + tslot + [s[0] for s in seqs] + starts + [s[1] for s in seqs]
+                + wants)
         total = len(flat)
         h[:total] = torch.tensor(flat, dtype=torch.int32)
         self.dev[:total].copy_(h[:total], non_blocking=True)
@@ -78,7 +82,8 @@ class StepBuffers:
         new = [len(s[2]) for s in seqs]
         return StepContext(
             T=T, B=B, tok_ids=d[o_ids:o_ids + T], tok_seq=d[o_seq:o_seq + T],
-            tok_pos=d[o_pos:o_pos + T], seq_slot=d[o_slot:o_slot + B],
+            tok_pos=d[o_pos:o_pos + T], tok_slot=d[o_tslot:o_tslot + T],
+            seq_slot=d[o_slot:o_slot + B],
             seq_start=d[o_start:o_start + B + 1], seq_past=d[o_past:o_past + B],
             want_rows=d[o_want:o_want + n_want], n_want=n_want, max_new=max(new),
             max_len=max(s[1] + len(s[2]) for s in seqs), decode=all(n == 1 for n in new),

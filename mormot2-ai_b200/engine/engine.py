@@ -164,7 +164,7 @@ class Engine:
         self.last_passes = len(passes)
         for seqs, dest in passes:
             ctx = self.buffers.fill(seqs)
-            self.last_h2d_bytes += 4 * (3 * ctx.T + 3 * ctx.B + 1 + ctx.n_want)
+            self.last_h2d_bytes += 4 * (4 * ctx.T + 3 * ctx.B + 1 + ctx.n_want)
             self.last_slots = ctx.seq_slot
             logits = self._forward(ctx)
             self.passes += 1

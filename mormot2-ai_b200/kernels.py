@@ -151,12 +151,12 @@ def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, 
         raise KernelError("q_norm and k_norm come together")
     wd = code_of(q_norm.dtype) if q_norm is not None else F32
     _call("rope", "mb_qk_norm_rope_store",
-          [_vp, _vp, _i, _ll, _vp, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _vp, _vp, _i, _i,
+          [_vp, _vp, _i, _ll, _vp, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _vp, _i, _i,
            _vp, _vp, _i, _i, _i, _i, _i, _vp],
           _ptr(qkv), _ptr(partial), partial.shape[0] if partial is not None else 0,
           partial.stride(0) if partial is not None else 0, _ptr(q_out), dtype_code,
           _ptr(q_norm), _ptr(k_norm), wd, float(eps),
-          _ptr(inv_freq), rot_dim, _ptr(step.tok_seq), _ptr(step.tok_pos), _ptr(step.seq_slot),
+          _ptr(inv_freq), rot_dim, _ptr(step.tok_slot), _ptr(step.tok_pos),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(line.k), _ptr(line.v),
           T, nh, nkv, hd, 1 if write_kv else 0, _stream())
 
@@ -280,11 +280,11 @@ def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, li
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert scratch.dtype == torch.float32 and scratch.is_contiguous()
     _call("attention_mma", "mb_attention_decode",
-          [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
+          [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
            _vp, _ll, _vp, _vp],
           _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
-          _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.tok_seq),
-          _ptr(step.tok_pos), _ptr(step.seq_slot), T, nh, nkv, hd, window, float(scale),
+          _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.tok_slot),
+          _ptr(step.tok_pos), T, nh, nkv, hd, window, float(scale),
           splits, _ptr(scratch), scratch.numel(), _ptr(error), _stream(), launches=2)
 
 

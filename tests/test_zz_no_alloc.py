@@ -17,7 +17,7 @@ from tests.gpu_helpers import DEV, fill_line, make_line, make_step
 pytestmark = pytest.mark.gpu
 
 _vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
-ARGTYPES = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
+ARGTYPES = [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
             _vp, _vp]
 LIMIT = 4 * 1024 * 1024          # MB_ATTENTION_DECODE_STATIC_FLOATS
 
@@ -32,7 +32,7 @@ def static_entry():
 def call_static(fn, q, out, step, line, nh, nkv, hd, window, scale, splits):
     return fn(q.data_ptr(), nh * hd, out.data_ptr(), out.stride(0), line.k.data_ptr(),
               line.v.data_ptr(), line.page_table.data_ptr(), line.max_pages, line.ring_pages,
-              step.tok_seq.data_ptr(), step.tok_pos.data_ptr(), step.seq_slot.data_ptr(),
+              step.tok_slot.data_ptr(), step.tok_pos.data_ptr(),
               out.shape[0], nh, nkv, hd, window, scale, splits, None,
               torch.cuda.current_stream().cuda_stream)
 
