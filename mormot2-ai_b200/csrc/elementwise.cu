@@ -105,20 +105,17 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partial, int
       const int c = (i * RMS_THREADS + threadIdx.x) * 4;
       if (c >= H) continue;
       const float* pp = partial + (size_t)src * H + c;
-      int p = 0;
-      for (; p + 4 <= parts; p += 4) {  // four loads in flight, added in split order
-        const float4 a0 = __ldg((const float4*)(pp + (size_t)p * part_stride));
-        const float4 a1 = __ldg((const float4*)(pp + (size_t)(p + 1) * part_stride));
-        const float4 a2 = __ldg((const float4*)(pp + (size_t)(p + 2) * part_stride));
-        const float4 a3 = __ldg((const float4*)(pp + (size_t)(p + 3) * part_stride));
-        v[i].x = (((v[i].x + a0.x) + a1.x) + a2.x) + a3.x;
-        v[i].y = (((v[i].y + a0.y) + a1.y) + a2.y) + a3.y;
-        v[i].z = (((v[i].z + a0.z) + a1.z) + a2.z) + a3.z;
-        v[i].w = (((v[i].w + a0.w) + a1.w) + a2.w) + a3.w;
-      }
-      for (; p < parts; ++p) {
-        const float4 a = __ldg((const float4*)(pp + (size_t)p * part_stride));
-        v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
+      // up to eight loads in flight at once, then added in split order
+      for (int p0 = 0; p0 < parts; p0 += 8) {
+        float4 a[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (p0 + j < parts) a[j] = __ldg((const float4*)(pp + (size_t)(p0 + j) * part_stride));
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (p0 + j < parts) {
+            v[i].x += a[j].x; v[i].y += a[j].y; v[i].z += a[j].z; v[i].w += a[j].w;
+          }
       }
       *(float4*)(xr + c) = v[i];
     }

@@ -44,6 +44,7 @@ enum { TC_STORE = 0, TC_ADD = 1, TC_PARTIAL = 2, TC_SWIGLU = 3 };
 #define TC_THREADS 192
 #define TC_A_TILE (TC_BM * TC_BK * 2)  // what an MMA reads from a stage's first operand
 #define TC_MAX_STAGES 32
+#define TC_MAX_SPLITS 8
 #define TC_SMEM_MAX (227 * 1024)
 
 template <int BN> struct TcCfg {
@@ -650,6 +651,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     plan_stages(p, bn, 110 * 1024);
     if (workspace && epilogue != TC_SWIGLU && tiles128 <= sms && nkb >= 8) {
       int want = slots / tiles128;
+      if (want > TC_MAX_SPLITS) want = TC_MAX_SPLITS;  // what the consumer adds up in one round of loads
       if (want > nkb / 4) want = nkb / 4;
       const long long per = (long long)M * N;
       if (want > workspace_floats / per) want = (int)(workspace_floats / per);
