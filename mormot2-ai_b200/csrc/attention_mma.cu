@@ -1,14 +1,16 @@
 // Attention over the paged cache on the tensor cores (bfloat16 storage, float32 softmax and
 // accumulation), for head sizes 64 and 128.
 //
-// Decode (`mb_attention_decode`): one new token per sequence. The query heads that share a KV
-// head are the 16 rows of the m16n8k16 MMA, so the keys and values of a sequence are read
-// once for the whole group. The pages of a sequence are split over `splits` CTAs (grid.x), the
-// four warps of a CTA take pages in turn, every warp keeps an online softmax of its own, the
-// warps are merged in shared memory and the splits by a second kernel (the reference's
-// flash-decoding split + `attnmerge`, tools/cuda/ops.cu:325-329, :589-617 of the reference
-// project; its formula src/infer/mormot.ai.infer.backend.cpu.pas:1296-1353). The split count
-// is fixed by the cache's capacity, not by the lengths, so a captured launch stays valid.
+// Decode (`mb_attention_decode`, `mb_attention_decode_clusters`): one new token per sequence.
+// The query heads that share a KV head are the 16 rows of the m16n8k16 MMA, so the keys and
+// values of a sequence are read once for the whole group. The pages of a sequence are split
+// over `splits` CTAs (grid.x), the four warps of a CTA take 16 keys of every page each, every
+// warp keeps an online softmax of its own, the warps are merged in shared memory, and the
+// splits either by a second kernel through scratch memory or, as the CTAs of one thread-block
+// cluster, through each other's shared memory (the reference's flash-decoding split +
+// `attnmerge`, tools/cuda/ops.cu:325-329, :589-617 of the reference project; its formula
+// src/infer/mormot.ai.infer.backend.cpu.pas:1296-1353). The split count is fixed by the
+// cache's capacity, not by the lengths, so a captured launch stays valid.
 //
 // Operands go from global memory straight into MMA fragments with 16-byte loads: the sum over
 // the head dimension (for q·k) and over the keys (for p·v) does not care about order, so the
@@ -103,6 +105,12 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_
 
 #define DEC_STAGES 3
 
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
 // One CTA per (token, KV head [x 16 query heads of its group], split). Warp 4 streams the
 // pages of this split (every `splits`-th page of the sequence) into shared memory, a whole K
 // tile and a whole V tile per page (16 KB each for heads of 128) by bulk asynchronous copies,
@@ -114,7 +122,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    int max_pages, int ring_pages, const int* __restrict__ tok_slot,
                    const int* __restrict__ tok_pos, int nh,
                    int nkv, int window, float scale_log2, float* __restrict__ part_o,
-                   float* __restrict__ part_ml, int* __restrict__ error) {
+                   float* __restrict__ part_ml, bf16* __restrict__ out, int out_stride,
+                   int in_clusters, int* __restrict__ error) {
   constexpr int CH = HD / 32;  // 32-dim chunks of q·k
   constexpr int DB = HD / 64;  // 64-dim blocks of p·v
   constexpr uint32_t TILE = MB_PAGE * HD * 2;  // bytes of a page's keys (or values)
@@ -289,6 +298,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   float* sm_o = (float*)dec_smem;                       // [DEC_WARPS][16][HD]
   float* sm_m = sm_o + DEC_WARPS * 16 * HD;             // [DEC_WARPS][16]
   float* sm_l = sm_m + DEC_WARPS * 16;                  // [DEC_WARPS][16]
+  float* sm_c = sm_l + DEC_WARPS * 16;                  // [16][HD] the CTA's own result
+  float* sm_cml = sm_c + 16 * HD;                       // [16] its maxima, [16] its sums
   if (warp < DEC_WARPS) {
     if (c == 0) {
       sm_m[warp * 16 + r] = m0;
@@ -322,12 +333,47 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
         acc += sm_o[(w * 16 + row) * HD + d] * f;
       }
     }
-    const size_t at = ((size_t)t * nh + h0 + row) * S + s;
-    part_o[at * HD + d] = acc;
-    if (d == 0) {
-      part_ml[at * 2] = M;
-      part_ml[at * 2 + 1] = L;
+    if (!in_clusters) {  // through the caller's scratch: the merge kernel adds the splits up
+      const size_t at = ((size_t)t * nh + h0 + row) * S + s;
+      part_o[at * HD + d] = acc;
+      if (d == 0) {
+        part_ml[at * 2] = M;
+        part_ml[at * 2 + 1] = L;
+      }
+    } else if (S == 1) {
+      out[(size_t)t * out_stride + (size_t)(h0 + row) * HD + d] = __float2bfloat16_rn(acc / L);
+    } else {
+      sm_c[row * HD + d] = acc;
+      if (d == 0) {
+        sm_cml[row] = M;
+        sm_cml[16 + row] = L;
+      }
     }
+  }
+  if (in_clusters && S > 1) {
+    // The splits of a (token, group) are the CTAs of one cluster: each adds up a share of the
+    // outputs from all the CTAs' shared memory, in split order.
+    cluster_sync_all();
+    const int total = rows_valid * HD, share = (total + S - 1) / S;
+    const int hi = min(total, (s + 1) * share);
+    const uint32_t c_addr = smem_u32(sm_c), ml_addr = smem_u32(sm_cml);
+    for (int idx = s * share + threadIdx.x; idx < hi; idx += blockDim.x) {
+      const int row = idx / HD, d = idx - row * HD;
+      float M = -INFINITY;
+      for (int k = 0; k < S; ++k)
+        M = fmaxf(M, ld_cluster_f32(cluster_addr_of(ml_addr + 4 * row, k)));
+      float L = 0.f, acc = 0.f;
+      for (int k = 0; k < S; ++k) {
+        const float m = ld_cluster_f32(cluster_addr_of(ml_addr + 4 * row, k));
+        const float l = ld_cluster_f32(cluster_addr_of(ml_addr + 4 * (16 + row), k));
+        const float v = ld_cluster_f32(cluster_addr_of(c_addr + 4 * (row * HD + d), k));
+        const float f = m == -INFINITY ? 0.f : exp2f(m - M);
+        L += l * f;
+        acc += v * f;
+      }
+      out[(size_t)t * out_stride + (size_t)(h0 + row) * HD + d] = __float2bfloat16_rn(acc / L);
+    }
+    cluster_sync_all();  // no CTA leaves while another may still read its shared memory
   }
 }
 
@@ -358,19 +404,8 @@ MB_EXPORT long long mb_attention_decode_scratch(int T, int nh, int hd, int split
   return (long long)T * nh * splits * (hd + 2);
 }
 
-// out[t, h, :] for every token t (each with its own sequence and position: a decode step, or
-// any few tokens). `splits` CTAs share a sequence's pages (CTA s takes the pages s, s + splits,
-// ...); the caller chooses it from the batch and the SM count, not from the lengths of the
-// moment, so that a captured launch stays valid. `scratch`: float32, at least
-// mb_attention_decode_scratch(...) values; its contents are not kept between calls. `error`:
-// a device word that receives 4 or 5 if a wait of the kernel's copy pipeline ran out.
-MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int out_stride,
-                                  const void* kpool, const void* vpool, const int* page_table,
-                                  int max_pages, int ring_pages, const int* tok_slot,
-                                  const int* tok_pos, int T, int nh, int nkv,
-                                  int hd, int window, float scale, int splits, float* scratch,
-                                  long long scratch_floats, int* error, void* stream) {
-  if (T <= 0) return 0;
+static int decode_checks(const void* q, int q_stride, const void* kpool, const void* vpool, int T,
+                         int nh, int nkv, int hd, int splits) {
   if (hd != 64 && hd != 128)
     MB_FAIL("mb_attention_decode: heads of %d values are not supported (64 or 128)", hd);
   if (nkv <= 0 || nh % nkv) MB_FAIL("mb_attention_decode: %d heads on %d KV heads", nh, nkv);
@@ -379,14 +414,19 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
     MB_FAIL("mb_attention_decode: the cache pools are not 16-byte aligned");
   if (((uintptr_t)q & 15) || (q_stride & 7))
     MB_FAIL("mb_attention_decode: q is not 16-byte aligned (stride %d)", q_stride);
-  const long long need = mb_attention_decode_scratch(T, nh, hd, splits);
-  if (scratch == nullptr || scratch_floats < need)
-    MB_FAIL("mb_attention_decode: %lld floats of scratch, %lld needed", scratch_floats, need);
-  const int G = nh / nkv, subs = (G + 15) / 16;
   if (T > 65535) MB_FAIL("mb_attention_decode: %d tokens are too many for one launch", T);
-  cudaStream_t s = (cudaStream_t)stream;
-  float* part_o = scratch;
-  float* part_ml = scratch + (size_t)T * nh * splits * hd;
+  return 0;
+}
+
+// in_clusters: the splits of a (token, group) form a cluster and are merged through their
+// shared memory (no scratch, no second kernel); else through part_o / part_ml
+static int decode_launch(const void* q, int q_stride, void* out, int out_stride,
+                         const void* kpool, const void* vpool, const int* page_table,
+                         int max_pages, int ring_pages, const int* tok_slot, const int* tok_pos,
+                         int T, int nh, int nkv, int hd, int window, float scale, int splits,
+                         float* part_o, float* part_ml, int in_clusters, int* error,
+                         cudaStream_t s) {
+  const int G = nh / nkv, subs = (G + 15) / 16;
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(splits, nkv * subs, T), mgrid(T, nh);
 #define GO(HD_)                                                                                \
@@ -399,16 +439,71 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
       if (e != cudaSuccess) MB_FAIL("mb_attention_decode: %s", cudaGetErrorString(e));         \
       configured = true;                                                                       \
     }                                                                                          \
-    mb_launch(attn_decode_kernel<HD_>, grid, dim3((DEC_WARPS + 1) * 32), smem, s,              \
-              (const bf16*)q, q_stride, (const bf16*)kpool, (const bf16*)vpool, page_table,    \
-              max_pages, ring_pages, tok_slot, tok_pos, nh, nkv, window, scale_log2,           \
-              part_o, part_ml, error);                                                         \
-    mb_launch(attn_merge_kernel<HD_>, mgrid, dim3(HD_), 0, s, (const float*)part_o,            \
-              (const float*)part_ml, splits, (bf16*)out, out_stride, nh);                      \
+    if (in_clusters && splits > 1) {                                                           \
+      mb_launch_clusters(attn_decode_kernel<HD_>, grid, dim3((DEC_WARPS + 1) * 32), smem, s,   \
+                         splits, (const bf16*)q, q_stride, (const bf16*)kpool,                 \
+                         (const bf16*)vpool, page_table, max_pages, ring_pages, tok_slot,      \
+                         tok_pos, nh, nkv, window, scale_log2, part_o, part_ml, (bf16*)out,    \
+                         out_stride, 1, error);                                                \
+    } else {                                                                                   \
+      mb_launch(attn_decode_kernel<HD_>, grid, dim3((DEC_WARPS + 1) * 32), smem, s,            \
+                (const bf16*)q, q_stride, (const bf16*)kpool, (const bf16*)vpool, page_table,  \
+                max_pages, ring_pages, tok_slot, tok_pos, nh, nkv, window, scale_log2, part_o, \
+                part_ml, (bf16*)out, out_stride, in_clusters, error);                          \
+      if (!in_clusters)                                                                        \
+        mb_launch(attn_merge_kernel<HD_>, mgrid, dim3(HD_), 0, s, (const float*)part_o,        \
+                  (const float*)part_ml, splits, (bf16*)out, out_stride, nh);                  \
+    }                                                                                          \
   }
   if (hd == 64) GO(64) else GO(128)
 #undef GO
   MB_CHECK_LAUNCH("mb_attention_decode");
+}
+
+// out[t, h, :] for every token t (each with its own sequence and position: a decode step, or
+// any few tokens). `splits` CTAs share a sequence's pages (CTA s takes the pages s, s + splits,
+// ...); the caller chooses it from the batch and the SM count, not from the lengths of the
+// moment, so that a captured launch stays valid. The splits leave their partial results in
+// `scratch` (float32, at least mb_attention_decode_scratch(...) values; its contents are not
+// kept between calls) and a second kernel adds them up. `error`: a device word that receives
+// 4 or 5 if a wait of the kernel's copy pipeline ran out.
+MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int out_stride,
+                                  const void* kpool, const void* vpool, const int* page_table,
+                                  int max_pages, int ring_pages, const int* tok_slot,
+                                  const int* tok_pos, int T, int nh, int nkv,
+                                  int hd, int window, float scale, int splits, float* scratch,
+                                  long long scratch_floats, int* error, void* stream) {
+  if (T <= 0) return 0;
+  if (decode_checks(q, q_stride, kpool, vpool, T, nh, nkv, hd, splits)) return -1;
+  const long long need = mb_attention_decode_scratch(T, nh, hd, splits);
+  if (scratch == nullptr || scratch_floats < need)
+    MB_FAIL("mb_attention_decode: %lld floats of scratch, %lld needed", scratch_floats, need);
+  return decode_launch(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
+                       ring_pages, tok_slot, tok_pos, T, nh, nkv, hd, window, scale, splits,
+                       scratch, scratch + (size_t)T * nh * splits * hd, 0, error,
+                       (cudaStream_t)stream);
+}
+
+// The same with the splits of a (token, group of heads) as the CTAs of one thread-block
+// cluster: they add their partial results up through each other's shared memory, so there is
+// no scratch and no second kernel. At most MB_DECODE_CLUSTER_SPLITS splits (the portable
+// cluster size); one split writes its result directly.
+#define MB_DECODE_CLUSTER_SPLITS 8
+MB_EXPORT int mb_attention_decode_clusters(const void* q, int q_stride, void* out,
+                                           int out_stride, const void* kpool, const void* vpool,
+                                           const int* page_table, int max_pages, int ring_pages,
+                                           const int* tok_slot, const int* tok_pos, int T,
+                                           int nh, int nkv, int hd, int window, float scale,
+                                           int splits, int* error, void* stream) {
+  if (T <= 0) return 0;
+  if (decode_checks(q, q_stride, kpool, vpool, T, nh, nkv, hd, splits)) return -1;
+  if (splits > MB_DECODE_CLUSTER_SPLITS)
+    MB_FAIL("mb_attention_decode_clusters: %d splits (a cluster holds at most %d)", splits,
+            MB_DECODE_CLUSTER_SPLITS);
+  if (((uintptr_t)out & 1)) MB_FAIL("mb_attention_decode_clusters: out is not aligned");
+  return decode_launch(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
+                       ring_pages, tok_slot, tok_pos, T, nh, nkv, hd, window, scale, splits,
+                       nullptr, nullptr, 1, error, (cudaStream_t)stream);
 }
 
 // ------------------------------------------------------------------ prefill

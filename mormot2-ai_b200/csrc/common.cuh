@@ -68,6 +68,27 @@ static cudaError_t mb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// The same with the CTAs of the grid's x direction in clusters of `cluster_x` (which divides it).
+template <typename... KArgs, typename... Args>
+static cudaError_t mb_launch_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, int cluster_x, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster_x;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = mb_pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 #define MB_DEFINE_LAST_ERROR \
   MB_EXPORT const char* mb_last_error() { return g_mb_error; }
 

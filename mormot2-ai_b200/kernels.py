@@ -288,6 +288,23 @@ def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, li
           splits, _ptr(scratch), scratch.numel(), _ptr(error), _stream(), launches=2)
 
 
+def attention_decode_clusters(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh,
+                              nkv, hd, window: int, scale: float, splits: int,
+                              error: Optional[torch.Tensor] = None) -> None:
+    """``attention_decode`` with the splits of a (token, group of heads) as one thread-block
+    cluster that merges through its shared memory: no scratch, one kernel; at most 8 splits."""
+    T = out.shape[0]
+    _contig(out, "out")
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    _call("attention_mma", "mb_attention_decode_clusters",
+          [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
+           _vp, _vp],
+          _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
+          _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.tok_slot),
+          _ptr(step.tok_pos), T, nh, nkv, hd, window, float(scale), splits, _ptr(error),
+          _stream())
+
+
 def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv,
                       hd, window: int, scale: float,
                       error: Optional[torch.Tensor] = None) -> None:

@@ -10,14 +10,15 @@ from .. import kernels as K
 from ..cache.pages import pages_for
 
 FAST_HEAD_DIMS = (64, 128)
-MAX_DECODE_SPLITS = 16
+MAX_DECODE_SPLITS = 8       # the splits of a sequence are one thread-block cluster
 
 
 def decode_splits(line, T: int, nh: int, nkv: int, sms: int, window: int) -> int:
     """Over how many CTAs the pages of a sequence are dealt out in a decode step of T tokens.
     Every CTA pays a fixed price (index loads before its first key, the merge at its end), so
-    few, long CTAs win: as many as give one round of two CTAs per SM, at most 16 (beyond that the
-    merge of the partial results costs more than the shorter CTAs save: measured at batch 1),
+    few, long CTAs win: as many as give one round of two CTAs per SM, at most 8 (the splits of a
+    sequence form a thread-block cluster that merges through shared memory, and beyond that the
+    merge costs more than the shorter CTAs save: measured at batch 1),
     and no more than the most pages that a sequence can hold in this line (the lengths of the
     moment do not count: a captured launch must stay valid as sequences grow)."""
     pages = line.max_pages
@@ -34,11 +35,8 @@ def run(rt, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> bool:
         return False
     if step.decode:
         splits = decode_splits(line, step.T, nh, nkv, rt.sms, window)
-        need = step.T * nh * splits * (hd + 2)
-        if rt.workspace is None or rt.workspace.numel() < need:
-            return False
-        K.attention_decode(q, q_stride, out, step, line, nh, nkv, hd, window, scale, splits,
-                           rt.workspace, rt.error_word)
+        K.attention_decode_clusters(q, q_stride, out, step, line, nh, nkv, hd, window, scale,
+                                    splits, rt.error_word)
         return True
     if out.stride(0) % 8 or out.data_ptr() % 16:
         return False

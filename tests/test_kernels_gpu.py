@@ -187,7 +187,8 @@ def attention_reference(q, keys, values, nh, nkv, hd, pos, window, scale):
 
 def run_attention(kind, q, out, step, line, nh, nkv, hd, window, scale, splits=None):
     """The general kernel ("simt") or the tensor-core kernel for single tokens ("decode", with
-    the sequence's pages shared out over `splits` CTAs)."""
+    the sequence's pages shared out over `splits` CTAs; "decode_clusters": the same with the
+    splits merged inside a thread-block cluster)."""
     if kind == "simt":
         K.attention_simt(q, nh * hd, out, step, line, nh, nkv, hd, window, scale)
         return
@@ -200,6 +201,12 @@ def run_attention(kind, q, out, step, line, nh, nkv, hd, window, scale, splits=N
         assert int(error.item()) == 0
         return
     splits = splits or 3
+    if kind == "decode_clusters":
+        error = torch.zeros(1, dtype=torch.int32, device=DEV)
+        K.attention_decode_clusters(q, nh * hd, out, step, line, nh, nkv, hd, window, scale,
+                                    splits, error)
+        assert int(error.item()) == 0
+        return
     scratch = torch.empty(out.shape[0] * nh * splits * (hd + 2) + 5, device=DEV)
     error = torch.zeros(1, dtype=torch.int32, device=DEV)
     K.attention_decode(q, nh * hd, out, step, line, nh, nkv, hd, window, scale, splits, scratch,
@@ -214,6 +221,11 @@ ATTENTION_CASES = [("simt", 4, 2, 16, "float32"), ("simt", 6, 1, 48, "float32"),
                    ("decode", 8, 2, 128, "bfloat16"), ("decode", 16, 2, 64, "bfloat16"),
                    ("decode", 3, 3, 64, "bfloat16"), ("decode", 40, 2, 128, "bfloat16"),
                    ("decode", 7, 1, 128, "bfloat16"),
+                   ("decode_clusters", 8, 2, 128, "bfloat16"),
+                   ("decode_clusters", 16, 2, 64, "bfloat16"),
+                   ("decode_clusters", 3, 3, 64, "bfloat16"),
+                   ("decode_clusters", 40, 2, 128, "bfloat16"),
+                   ("decode_clusters", 7, 1, 128, "bfloat16"),
                    ("prefill", 8, 2, 128, "bfloat16"), ("prefill", 16, 2, 64, "bfloat16"),
                    ("prefill", 3, 3, 64, "bfloat16"), ("prefill", 7, 1, 128, "bfloat16"),
                    ("prefill_tc", 8, 2, 128, "bfloat16"), ("prefill_tc", 7, 1, 128, "bfloat16"),
@@ -243,7 +255,7 @@ def test_attention_over_the_paged_cache(kind, nh, nkv, hd, dtype):
         q = torch.tensor(rng.standard_normal((T, nh * hd)), dtype=torch.float32).to(dt)
         out = torch.empty(T, nh * hd, dtype=dt, device=DEV)
         scale = 1.0 / math.sqrt(hd)
-        for splits in ((1, 3, 4, 7) if kind == "decode" else (None,)):
+        for splits in ((1, 3, 4, 7, 8) if kind.startswith("decode") else (None,)):
             out.zero_()
             run_attention(kind, q.to(DEV), out, step, line, nh, nkv, hd, window, scale, splits)
             got = out.float().cpu().numpy().reshape(T, nh, hd)
@@ -258,6 +270,8 @@ def test_attention_over_the_paged_cache(kind, nh, nkv, hd, dtype):
 
 @pytest.mark.parametrize("kind,hd,dtype", [("simt", 32, "float32"), ("simt", 32, "bfloat16"),
                                            ("decode", 64, "bfloat16"), ("decode", 128, "bfloat16"),
+                                           ("decode_clusters", 64, "bfloat16"),
+                                           ("decode_clusters", 128, "bfloat16"),
                                            ("prefill", 64, "bfloat16"), ("prefill", 128, "bfloat16"),
                                            ("prefill_tc", 128, "bfloat16")])
 def test_attention_finds_a_far_key_and_respects_the_windows_edge(kind, hd, dtype):
