@@ -5,14 +5,18 @@
 //
 // A CTA takes 128 consecutive new tokens of one sequence and one query head and walks the
 // pages of the cache that these tokens see (64 keys a page):
-//   warp 0      loads Q once, then K and V of page after page into rings of two stages each
-//               (K one page ahead of V: its stage is free again after the first product);
-//   warp 1      issues S = Q·Kᵀ (128 x 64), and when P is ready O += P·V (128 x 128);
+//   warp 0      loads Q once, then K and V of page after page into rings of three and two stages
+//               (K ahead of V: its stage is free again after the first product);
+//   warp 1      issues S = Q·Kᵀ (128 x 64) two pages ahead into one of two S buffers in tensor
+//               memory, and when P of a page is ready O += P·V (128 x 128) with P as the
+//               operand that lies in tensor memory;
 //   warps 2-5   read S, mask it (causal bound and window by position), keep the row maximum
-//               and sum, write P = exp2(S - max) as bfloat16 into shared memory for the second
-//               product, and rescale O in tensor memory when a row's maximum has grown by
-//               more than 2^8 since O was last rescaled (else the old maximum stays the
-//               reference: the result is the same, the sum just carries the factor);
+//               and sum, and write P = exp2(S - max) as bfloat16 over the S they have just read
+//               (the second product takes it from there), so that the softmax of a page never
+//               waits for the product of the page before; they rescale O in tensor memory only
+//               when a row's maximum has grown by more than 2^8 since O was last rescaled
+//               (else the old maximum stays the reference: the result is the same, the sum
+//               just carries the factor), and only then wait for the products in flight;
 //               at the end they divide O by the row sums and store it.
 // Two CTAs share an SM, so that one CTA's products run under the other's softmax.
 //
@@ -26,15 +30,15 @@ typedef __nv_bfloat16 bf16;
 
 #define AT_ROWS 128
 #define AT_HD 128
-#define AT_STAGES 2
+#define AT_K_STAGES 3
+#define AT_V_STAGES 2
 #define AT_THREADS 192
 #define AT_Q_BYTES (AT_ROWS * AT_HD * 2)    // 32 KB: two 128 x 64 halves
 #define AT_KV_BYTES (MB_PAGE * AT_HD * 2)   // 16 KB: two 64 x 64 halves
-#define AT_P_BYTES (AT_ROWS * MB_PAGE * 2)  // 16 KB: 128 rows of 64 keys
 // no slack for alignment: two CTAs must fit in one SM; the kernel checks that its dynamic
 // shared memory starts on a 1024-byte boundary (it does when there is no static shared memory)
-#define AT_SMEM (AT_Q_BYTES + AT_STAGES * 2 * AT_KV_BYTES + AT_P_BYTES + 256)
-#define AT_TMEM_COLS 256                    // S: 64 columns, O: 128 columns
+#define AT_SMEM (AT_Q_BYTES + (AT_K_STAGES + AT_V_STAGES) * AT_KV_BYTES + 256)
+#define AT_TMEM_COLS 256                    // two S buffers of 64 columns, O: 128 columns
 
 // Operand descriptor of an MN-major tile written by TMA with the 128-byte swizzle: rows of 64
 // values (128 bytes) are consecutive values of the K dimension (here: keys), 8 rows make a
@@ -76,6 +80,66 @@ __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// 64 consecutive float32 columns of this thread's TMEM lane: four loads in flight, one wait.
+// The loaded registers pass through the wait (and through empty statements after it) so that
+// no use of them can be scheduled before it.
+#define AT_LD16(R, OFF)                                                                          \
+  asm volatile(                                                                                  \
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32"                                                   \
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"         \
+      : "=r"(R[0]), "=r"(R[1]), "=r"(R[2]), "=r"(R[3]), "=r"(R[4]), "=r"(R[5]), "=r"(R[6]),      \
+        "=r"(R[7]), "=r"(R[8]), "=r"(R[9]), "=r"(R[10]), "=r"(R[11]), "=r"(R[12]), "=r"(R[13]),  \
+        "=r"(R[14]), "=r"(R[15])                                                                 \
+      : "r"(taddr + OFF))
+#define AT_HOLD16(TEXT, R)                                                                       \
+  asm volatile(TEXT                                                                              \
+               : "+r"(R[0]), "+r"(R[1]), "+r"(R[2]), "+r"(R[3]), "+r"(R[4]), "+r"(R[5]),         \
+                 "+r"(R[6]), "+r"(R[7]), "+r"(R[8]), "+r"(R[9]), "+r"(R[10]), "+r"(R[11]),       \
+                 "+r"(R[12]), "+r"(R[13]), "+r"(R[14]), "+r"(R[15])                              \
+               :                                                                                 \
+               : "memory")
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float* v) {
+  uint32_t a[16], b[16], c[16], d[16];
+  AT_LD16(a, 0);
+  AT_LD16(b, 16);
+  AT_LD16(c, 32);
+  AT_LD16(d, 48);
+  AT_HOLD16("tcgen05.wait::ld.sync.aligned;", a);
+  AT_HOLD16("", b);
+  AT_HOLD16("", c);
+  AT_HOLD16("", d);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    v[i] = __uint_as_float(a[i]);
+    v[16 + i] = __uint_as_float(b[i]);
+    v[32 + i] = __uint_as_float(c[i]);
+    v[48 + i] = __uint_as_float(d[i]);
+  }
+}
+
+// 16 packed words (32 bfloat16 values) into this thread's TMEM lane
+__device__ __forceinline__ void tmem_st16_u32(uint32_t taddr, const uint32_t* w) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n"
+      ::"r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]),
+        "r"(w[7]), "r"(w[8]), "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]),
+        "r"(w[14]), "r"(w[15])
+      : "memory");
+}
+
+// D[tmem] (+)= A[tmem] · B[smem]: the first operand (128 rows x 16 bfloat16 values, two values
+// a 32-bit column, 8 columns) lies in tensor memory. Issued by one thread.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
                        const __grid_constant__ CUtensorMap tmK,
@@ -92,13 +156,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
   }
   const uint32_t sQ = raw;
   const uint32_t sK = sQ + AT_Q_BYTES;                  // [stage][16 KB]
-  const uint32_t sV = sK + AT_STAGES * AT_KV_BYTES;
-  const uint32_t sP = sV + AT_STAGES * AT_KV_BYTES;
-  const uint32_t bars = sP + AT_P_BYTES;
-  const uint32_t q_full = bars, k_full0 = bars + 8, k_empty0 = k_full0 + 8 * AT_STAGES;
-  const uint32_t v_full0 = k_empty0 + 8 * AT_STAGES, v_empty0 = v_full0 + 8 * AT_STAGES;
-  const uint32_t s_full = v_empty0 + 8 * AT_STAGES, s_free = s_full + 8, p_full = s_full + 16;
-  const uint32_t o_done = s_full + 24, slot = s_full + 32;
+  const uint32_t sV = sK + AT_K_STAGES * AT_KV_BYTES;
+  const uint32_t bars = sV + AT_V_STAGES * AT_KV_BYTES;
+  const uint32_t q_full = bars, k_full0 = bars + 8, k_empty0 = k_full0 + 8 * AT_K_STAGES;
+  const uint32_t v_full0 = k_empty0 + 8 * AT_K_STAGES, v_empty0 = v_full0 + 8 * AT_V_STAGES;
+  const uint32_t s_full0 = v_empty0 + 8 * AT_V_STAGES;  // one for each of the two S buffers
+  const uint32_t p_full0 = s_full0 + 16;                // and for the P written over each
+  // the second product of page j done: barrier j % 2 (a waiter may have skipped the page
+  // before, and one barrier could then be two phases on, which a parity cannot tell)
+  const uint32_t o_done0 = p_full0 + 16, slot = o_done0 + 16;
   volatile uint32_t* slot_ptr = (volatile uint32_t*)(at_smem + (slot - raw));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -116,16 +182,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < AT_STAGES; ++i) {
+    for (int i = 0; i < AT_K_STAGES; ++i) {
       mbar_init(k_full0 + 8 * i, 1);
       mbar_init(k_empty0 + 8 * i, 1);
+    }
+    for (int i = 0; i < AT_V_STAGES; ++i) {
       mbar_init(v_full0 + 8 * i, 1);
       mbar_init(v_empty0 + 8 * i, 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(s_free, 4);
-    mbar_init(p_full, 4);
-    mbar_init(o_done, 1);
+    mbar_init(s_full0, 1);
+    mbar_init(s_full0 + 8, 1);
+    mbar_init(p_full0, 4);
+    mbar_init(p_full0 + 8, 4);
+    mbar_init(o_done0, 1);
+    mbar_init(o_done0 + 8, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
@@ -136,7 +206,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *slot_ptr;
-  const uint32_t tS = tmem, tO = tmem + 64;
+  const uint32_t tS = tmem, tO = tmem + 128;  // S (and then P) of page j in tS + 64 * (j % 2)
   mb_grid_wait();  // q and the newest keys and values come from the kernel before
   mb_grid_launch_next();
 
@@ -145,8 +215,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
       mbar_expect_tx(q_full, AT_Q_BYTES);
       tma_load_2d(sQ, &tmQ, h * AT_HD, start + row0, q_full);
       tma_load_2d(sQ + AT_Q_BYTES / 2, &tmQ, h * AT_HD + 64, start + row0, q_full);
-      // K of a page is free again after the first product of the page two before, V only after
-      // its second product: K runs one page ahead of V so that neither load waits for the other
+      // the first products run two pages ahead of the second ones: so do the loads of K
       auto row_of = [&](int j) {
         const int p = page0 + j;
         const int page =
@@ -154,17 +223,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
         return (page * nkv + g) * MB_PAGE;
       };
       auto load_k = [&](int j) {
-        const int st = j % AT_STAGES, y = row_of(j);
-        mbar_wait(k_empty0 + 8 * st, ((j / AT_STAGES) & 1) ^ 1, error, 11);
+        const int st = j % AT_K_STAGES, y = row_of(j);
+        mbar_wait(k_empty0 + 8 * st, ((j / AT_K_STAGES) & 1) ^ 1, error, 11);
         mbar_expect_tx(k_full0 + 8 * st, AT_KV_BYTES);
         tma_load_2d(sK + st * AT_KV_BYTES, &tmK, 0, y, k_full0 + 8 * st);
         tma_load_2d(sK + st * AT_KV_BYTES + AT_KV_BYTES / 2, &tmK, 64, y, k_full0 + 8 * st);
       };
       load_k(0);
+      if (n_pages > 1) load_k(1);
       for (int j = 0; j < n_pages; ++j) {
-        if (j + 1 < n_pages) load_k(j + 1);
-        const int st = j % AT_STAGES, y = row_of(j);
-        mbar_wait(v_empty0 + 8 * st, ((j / AT_STAGES) & 1) ^ 1, error, 10);
+        if (j + 2 < n_pages) load_k(j + 2);
+        const int st = j % AT_V_STAGES, y = row_of(j);
+        mbar_wait(v_empty0 + 8 * st, ((j / AT_V_STAGES) & 1) ^ 1, error, 10);
         mbar_expect_tx(v_full0 + 8 * st, AT_KV_BYTES);
         tma_load_2d(sV + st * AT_KV_BYTES, &tmV, 0, y, v_full0 + 8 * st);
         tma_load_2d(sV + st * AT_KV_BYTES + AT_KV_BYTES / 2, &tmV, 64, y, v_full0 + 8 * st);
@@ -175,41 +245,49 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
       constexpr uint32_t idesc_s = umma_idesc_bf16(AT_ROWS, MB_PAGE);             // K-major both
       constexpr uint32_t idesc_o = umma_idesc_bf16(AT_ROWS, 64) | (1u << 16);     // B MN-major
       mbar_wait(q_full, 0, error, 12);
-      // S of page j + 1 is issued before the wait for P of page j, so that the softmax of a
-      // page finds its scores ready and the first product runs under the softmax before it
+      // S of page j goes into buffer j % 2, which held S and then P of page j - 2
       auto issue_s = [&](int j) {
-        const int st = j % AT_STAGES;
-        mbar_wait(k_full0 + 8 * st, (j / AT_STAGES) & 1, error, 13);
-        if (j > 0) mbar_wait(s_free, (j - 1) & 1, error, 14);  // S of the page before was read
+        const int st = j % AT_K_STAGES;
+        mbar_wait(k_full0 + 8 * st, (j / AT_K_STAGES) & 1, error, 13);
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < AT_HD / 16; ++k) {
           const uint64_t da = umma_desc_k128(sQ + (k / 4) * (AT_Q_BYTES / 2) + (k % 4) * 32);
           const uint64_t db =
               umma_desc_k128(sK + st * AT_KV_BYTES + (k / 4) * (AT_KV_BYTES / 2) + (k % 4) * 32);
-          umma_bf16(tS, da, db, idesc_s, k > 0);
+          umma_bf16(tS + 64 * (j & 1), da, db, idesc_s, k > 0);
         }
         umma_commit(k_empty0 + 8 * st);  // K of this page has been read
-        umma_commit(s_full);
+        umma_commit(s_full0 + 8 * (j & 1));
       };
       issue_s(0);
+      if (n_pages > 1) issue_s(1);
       for (int j = 0; j < n_pages; ++j) {
-        const int st = j % AT_STAGES;
-        if (j + 1 < n_pages) issue_s(j + 1);
-        mbar_wait(v_full0 + 8 * st, (j / AT_STAGES) & 1, error, 9);
-        mbar_wait(p_full, j & 1, error, 15);  // P of this page is in shared memory
+        const int st = j % AT_V_STAGES;
+        mbar_wait(v_full0 + 8 * st, (j / AT_V_STAGES) & 1, error, 9);
+        // P of this page is in tensor memory (a barrier per buffer: the softmax may be a page
+        // ahead of this wait, and one barrier would then be two phases on)
+        mbar_wait(p_full0 + 8 * (j & 1), (j >> 1) & 1, error, 15);
         tc_fence_after_sync();
+        const uint32_t tP = tS + 64 * (j & 1);
 #pragma unroll
         for (int half = 0; half < 2; ++half)
 #pragma unroll
           for (int k = 0; k < MB_PAGE / 16; ++k) {
-            const uint64_t da = umma_desc_k128(sP + k * 32);
             const uint64_t db = umma_desc_mn128(
                 sV + st * AT_KV_BYTES + half * (AT_KV_BYTES / 2) + k * 2048, AT_KV_BYTES / 2);
-            umma_bf16(tO + half * 64, da, db, idesc_o, (j | k) != 0);
+            umma_bf16_ts(tO + half * 64, tP + 8 * k, db, idesc_o, (j | k) != 0);
           }
         umma_commit(v_empty0 + 8 * st);  // V of this page has been read
-        umma_commit(o_done);
+        umma_commit(o_done0 + 8 * (j & 1));
+        if (j + 2 < n_pages) {
+          // S of page j + 2 overwrites the P that the product just issued reads as an operand:
+          // nothing orders a later instruction's result after an earlier one's operand read in
+          // tensor memory, so wait until that product is done (S of page j + 1 is long ready,
+          // the softmax does not wait for this)
+          mbar_wait(o_done0 + 8 * (j & 1), (j >> 1) & 1, error, 14);
+          issue_s(j + 2);
+        }
       }
     }
   } else {
@@ -220,40 +298,39 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     float m_ref = -INFINITY, l = 0.f;
     for (int j = 0; j < n_pages; ++j) {
-      mbar_wait(s_full, j & 1, error, 16);
+      const uint32_t tSj = tS + 64 * (j & 1) + lane_addr;
+      mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, error, 16);
       tc_fence_after_sync();
       float s[MB_PAGE];
-#pragma unroll
-      for (int c0 = 0; c0 < MB_PAGE; c0 += 16) tmem_ld16(tS + lane_addr + c0, s + c0);
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_free);
+      tmem_ld64(tSj, s);
       const int key0 = (page0 + j) * MB_PAGE;
-      float mx = -INFINITY;
       // a page that every row of the warp sees whole needs no mask (uniform over the warp)
       const bool whole = key0 + MB_PAGE - 1 <= pos - lane &&
                          (window == 0 || key0 >= lo + (31 - lane));
-      if (whole) {
-#pragma unroll
-        for (int c = 0; c < MB_PAGE; ++c) {
-          s[c] *= scale_log2;
-          mx = fmaxf(mx, s[c]);
-        }
-      } else {
+      if (!whole) {
 #pragma unroll
         for (int c = 0; c < MB_PAGE; ++c) {
           const int key = key0 + c;
-          s[c] = (key >= lo && key <= pos) ? s[c] * scale_log2 : -INFINITY;
-          mx = fmaxf(mx, s[c]);
+          if (!(key >= lo && key <= pos)) s[c] = -INFINITY;
         }
       }
+      // four chains, so that the maximum (and the sum below) does not wait on itself
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < MB_PAGE; ++c) {
+        s[c] *= scale_log2;
+        mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // O is rescaled only when this row's maximum has grown by more than 2^8 (or appears for
       // the first time); until then the old reference stays and P may reach 2^8
       const bool grow = mx > m_ref + 8.0f || (m_ref == -INFINITY && mx > -INFINITY);
-      if (j > 0) mbar_wait(o_done, (j - 1) & 1, error, 17);  // O and P are free again
       if (__any_sync(0xffffffffu, grow)) {
         const float f = grow ? (m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx)) : 1.f;
         if (j > 0) {
+          // the second product of the page before adds into O: it must be done (the one of
+          // this page waits for the P written below)
+          mbar_wait(o_done0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, error, 17);
           tc_fence_after_sync();
 #pragma unroll 1
           for (int c0 = 0; c0 < AT_HD; c0 += 16) {
@@ -263,35 +340,34 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
             for (int i = 0; i < 16; ++i) o[i] *= f;
             tmem_st16(tO + lane_addr + c0, o);
           }
-          tmem_wait_st();
         }
         l *= f;
         if (grow) m_ref = mx;
       }
       const float ref = m_ref == -INFINITY ? 0.f : m_ref;
-      // P as the first operand of the second product: row `row` of a K-major tile of 128-byte
-      // rows with the 128-byte swizzle (the 16-byte chunk c goes to chunk c ^ (row % 8))
-      const uint32_t prow = sP + row * 128;
+      // P over the S just read, as the first operand of the second product: this thread's row,
+      // two bfloat16 values a column, keys in order
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {
-        uint32_t w[4];
+      for (int c16 = 0; c16 < 2; ++c16) {
+        uint32_t w[16];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float p0 = ex2(s[c8 * 8 + 2 * i] - ref), p1 = ex2(s[c8 * 8 + 2 * i + 1] - ref);
-          l += p0 + p1;
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = ex2(s[c16 * 32 + 2 * i] - ref), p1 = ex2(s[c16 * 32 + 2 * i + 1] - ref);
+          l4[i & 3] += p0 + p1;
           __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
           w[i] = *reinterpret_cast<uint32_t*>(&v);
         }
-        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(prow + ((c8 ^ (row & 7)) << 4)),
-                     "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
-                     : "memory");
+        tmem_st16_u32(tSj + 16 * c16, w);
       }
-      fence_async_smem();  // the tensor core reads P through the asynchronous proxy
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(p_full0 + 8 * (j & 1));
     }
-    mbar_wait(o_done, (n_pages - 1) & 1, error, 18);
+    // the last product done means all are (the tensor core works in the order of issue)
+    mbar_wait(o_done0 + 8 * ((n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1, error, 18);
     tc_fence_after_sync();
     const float inv = 1.0f / l;
     const bool mine = row0 + row < n_new;
