@@ -255,6 +255,50 @@ __device__ double block_sum_double(double v, double* sh) {
   return r;
 }
 
+// By a whole block: the sum of w[0 .. n) when `total_only`, else the first index whose running
+// sum (in index order) reaches `target` (strict: exceeds it), left in *found (n if none).
+// Every thread sums a contiguous run, one thread adds the runs up in order, the thread whose
+// run holds the target walks it. `runs` holds SAMPLE_THREADS doubles.
+__device__ double block_walk(const double* __restrict__ w, int n, double target, bool strict,
+                             bool total_only, double* runs, int* found) {
+  const int per = (n + blockDim.x - 1) / blockDim.x;
+  const int i0 = min(n, (int)threadIdx.x * per), i1 = min(n, i0 + per);
+  double mine = 0.0;
+  for (int i = i0; i < i1; ++i) mine += w[i];
+  runs[threadIdx.x] = mine;
+  if (threadIdx.x == 0) *found = n;
+  __syncthreads();
+  __shared__ double total_sh;
+  if (threadIdx.x == 0) {
+    double total = 0.0;
+    for (int t = 0; t < (int)blockDim.x; ++t) {
+      const double v = runs[t];
+      runs[t] = total;
+      total += v;
+    }
+    total_sh = total;
+  }
+  __syncthreads();
+  const double total = total_sh;
+  if (!total_only) {
+    const double before = runs[threadIdx.x];
+    const bool here = strict ? (target >= before && target < before + mine)
+                             : (target > before && target <= before + mine);
+    if (here) {
+      double cum = before;
+      for (int i = i0; i < i1; ++i) {
+        cum += w[i];
+        if (strict ? target < cum : cum >= target) {
+          atomicMin(found, i);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return total;
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, double inv_t,
                        int top_k, double top_p, double min_p,
@@ -267,6 +311,7 @@ sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, d
   __shared__ double dsh[33];
   __shared__ int count_sh;
   __shared__ int result_sh;
+  __shared__ double wsum[SAMPLE_THREADS];
   const float* row = logits + blockIdx.x * stride;
   unsigned long long* keys = scratch + blockIdx.x * scratch_stride;
   const Best best = block_argmax(row, V, sh);
@@ -274,36 +319,50 @@ sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, d
     if (threadIdx.x == 0) out[blockIdx.x] = best.i;
     return;
   }
-  double mine = 0.0;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) mine += weight_of(row[i], best.v, inv_t);
-  const double sum = block_sum_double(mine, dsh);
-  // weights relative to the best one (which weighs 1): p_i = w_i / sum
+  // the sum of all weights (relative to the best one, which weighs 1) is needed only for a
+  // top-p over the whole vocabulary: p_i = w_i / sum
+  const bool whole_mass = top_p < 1.0 && top_k == 0;
+  double sum = 0.0;
+  if (whole_mass) {
+    double mine = 0.0;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mine += weight_of(row[i], best.v, inv_t);
+    sum = block_sum_double(mine, dsh);
+  }
+  // A token is a candidate when its weight is at least t, tested on the exponent (no exp for
+  // the many that fail). The threshold goes down in small steps at first (each step is a pass
+  // over the row, but a step too far makes the sort below long), then in large ones.
   double t = (top_k > 0 || top_p < 1.0) ? 1e-3 : min_p;
+  double log_t = t > 0.0 ? log(t) : -INFINITY;
   int n = 0;
-  for (;;) {
+  for (int round = 0;; ++round) {
     int cnt = 0;
     double above = 0.0;
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const double w = weight_of(row[i], best.v, inv_t);
-      const bool finite = (__float_as_uint(row[i]) & 0x7f800000u) != 0x7f800000u;
-      if (finite && w >= t) { ++cnt; above += w; }
+      const float v = row[i];
+      const bool finite = (__float_as_uint(v) & 0x7f800000u) != 0x7f800000u;
+      const double x = ((double)v - (double)best.v) * inv_t;
+      if (finite && x >= log_t) {
+        ++cnt;
+        if (whole_mass) above += exp(x);
+      }
     }
-    above = block_sum_double(above, dsh);
+    if (whole_mass) above = block_sum_double(above, dsh);
     n = (int)(block_sum_double((double)cnt, dsh) + 0.5);
     bool enough = true;
     if (top_k > 0) enough = n >= top_k;
     else if (top_p < 1.0) enough = above >= top_p * sum;
     if (enough || t == 0.0) break;
-    t *= 1e-3;
+    t *= round < 6 ? 0.1 : 1e-3;
     if (t < 1e-300) t = 0.0;
+    log_t = t > 0.0 ? log(t) : -INFINITY;
   }
   // gather the candidates' keys, pad to a power of two with the largest key
   if (threadIdx.x == 0) count_sh = 0;
   __syncthreads();
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const double w = weight_of(row[i], best.v, inv_t);
-    const bool finite = (__float_as_uint(row[i]) & 0x7f800000u) != 0x7f800000u;
-    if (finite && w >= t) {
+    const float v = row[i];
+    const bool finite = (__float_as_uint(v) & 0x7f800000u) != 0x7f800000u;
+    if (finite && ((double)v - (double)best.v) * inv_t >= log_t) {
       const int at = atomicAdd(&count_sh, 1);
       keys[at] = ((unsigned long long)(~ordered_bits(row[i])) << 32) | (unsigned)i;
     }
@@ -328,6 +387,59 @@ sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, d
       __syncthreads();
     }
   }
+  // The candidates' weights in sorted order, once, next to the keys (there is room unless more
+  // than half of the vocabulary is a candidate: then one thread walks them as they are).
+  double* wts = 2 * (size_t)np <= scratch_stride ? (double*)(keys + np) : nullptr;
+  if (wts) {
+    for (int c = threadIdx.x; c < n; c += blockDim.x)
+      wts[c] = weight_of(row[(int)(keys[c] & 0xffffffffull)], best.v, inv_t);
+    __syncthreads();
+    auto id_of = [&](int c) { return (int)(keys[c] & 0xffffffffull); };
+    if (top_k > 0 && n > top_k) {
+      if (threadIdx.x == 0) {
+        int keep = top_k;
+        const float kth = row[id_of(top_k - 1)];
+        while (keep < n && row[id_of(keep)] == kth) ++keep;
+        count_sh = keep;
+      }
+      __syncthreads();
+      n = count_sh;
+      __syncthreads();
+    }
+    if (top_p < 1.0) {
+      const double mass = top_k > 0 ? block_walk(wts, n, 0.0, false, true, wsum, &count_sh) : sum;
+      block_walk(wts, n, top_p * mass, false, false, wsum, &count_sh);
+      n = min(n, count_sh + 1);
+      __syncthreads();
+    }
+    if (min_p > 0.0) {
+      // sorted by logit, so the weights do not rise: the first one below the bound ends the list
+      if (threadIdx.x == 0) count_sh = n;
+      __syncthreads();
+      const double bound = min_p * wts[0];
+      int first = n;
+      for (int c = 1 + threadIdx.x; c < n; c += blockDim.x)
+        if (!(wts[c] >= bound)) { first = c; break; }
+      if (first < n) atomicMin(&count_sh, first);
+      __syncthreads();
+      n = count_sh;
+      __syncthreads();
+    }
+    const double kept = block_walk(wts, n, 0.0, false, true, wsum, &count_sh);
+    if (threadIdx.x == 0) {
+      unsigned long long* st = states + state_index[blockIdx.x];
+      unsigned long long z = (*st += 0x9E3779B97F4A7C15ull);
+      z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+      z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+      z = z ^ (z >> 31);
+      dsh[0] = (double)(z >> 11) * (1.0 / 9007199254740992.0) * kept;
+    }
+    __syncthreads();
+    const double u = dsh[0];
+    __syncthreads();
+    block_walk(wts, n, u, true, false, wsum, &count_sh);
+    if (threadIdx.x == 0) result_sh = id_of(count_sh < n ? count_sh : 0);
+  } else
   if (threadIdx.x == 0) {
     auto id_of = [&](int c) { return (int)(keys[c] & 0xffffffffull); };
     auto w_of = [&](int c) { return weight_of(row[id_of(c)], best.v, inv_t); };
