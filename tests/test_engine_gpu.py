@@ -247,3 +247,44 @@ def test_layers_of_full_size_bfloat16_against_float32():
         assert rel(a, b) <= 3e-2, (step, rel(a, b))
     fast.rt.check()
     slow.rt.check()
+
+
+ODD_CONFIGS = [
+    # width, heads, kv heads, head size, feed-forward, vocabulary, layers, windows, tied
+    (80, 5, 5, 48, 200, 1000, 3, (0, 40, 0), True),        # no grouping, heads of 48
+    (72, 3, 1, 80, 104, 333, 2, (0, 0), True),             # heads of 80, an odd vocabulary
+    (100, 5, 1, 112, 90, 127, 2, (65, 0), False),          # a width that is no multiple of 8
+    (64, 2, 2, 256, 96, 260, 1, (0,), False),              # heads of 256
+    (136, 7, 7, 96, 72, 515, 2, (0, 130), True),           # seven heads of 96
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("sizes", ODD_CONFIGS, ids=[f"h{c[0]}_hd{c[3]}" for c in ODD_CONFIGS])
+def test_other_sizes_whole_and_decoded(sizes, dtype, tmp_path):
+    """Sizes that the four tiny configurations do not have (head sizes 48 to 256 in steps of 16,
+    odd head counts, widths and vocabularies off every power of two): a batch of two unequal
+    prompts, then tokens one by one, against the plain implementation."""
+    from mormot2_ai_b200 import Qwen3Config, write_random_model
+    from tests.plain import qwen3_plain as plain
+    hidden, nh, nkv, hd, inter, vocab, layers, windows, tied = sizes
+    cfg = Qwen3Config(vocab_size=vocab, hidden_size=hidden, num_hidden_layers=layers,
+                      num_attention_heads=nh, num_key_value_heads=nkv, head_dim=hd,
+                      intermediate_size=inter, max_position_embeddings=256, rms_norm_eps=1e-6,
+                      rope_theta=1e5, tie_word_embeddings=tied, layer_windows=windows)
+    folder = write_random_model(str(tmp_path / "m"), cfg, 11, std=0.05, norm_std=0.1)
+    pc, pw = plain.read_model_folder(folder)
+    eng = Engine.from_folder(folder, dtype=dtype, max_tokens=1024)
+    rng = np.random.default_rng(hidden)
+    seqs = [rng.integers(0, vocab, n).tolist() for n in (150, 67)]
+    refs = [plain.forward(pc, pw, ids) for ids in seqs]
+    heads = [130, 60]
+    slots = [eng.open() for _ in seqs]
+    out = eng.step([Entry(s, ids[:h], list(range(h))) for s, ids, h in zip(slots, seqs, heads)])
+    check(out.cpu().numpy(), np.concatenate([r[:h] for r, h in zip(refs, heads)]), dtype,
+          "prompts")
+    for t in range(7):
+        out = eng.step([Entry(s, [ids[h + t]]) for s, ids, h in zip(slots, seqs, heads)])
+        check(out.cpu().numpy(), np.stack([r[h + t] for r, h in zip(refs, heads)]), dtype,
+              f"decoded token {t}")
+    eng.rt.check()
