@@ -10,6 +10,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 
@@ -42,6 +43,7 @@ class StepBuffers:
         self.max_tokens, self.max_seqs = max_tokens, max_seqs
         self.size = 5 * max_tokens + 3 * max_seqs + 1
         self.host = torch.zeros(self.size, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()      # the same pinned memory, for vectorised filling
         self.dev = torch.zeros(self.size, dtype=torch.int32, device=device)
         self.copied = torch.cuda.Event()
         self.in_flight = False
@@ -57,29 +59,48 @@ class StepBuffers:
         h = self.host
         o_ids, o_seq, o_pos, o_tslot = 0, T, 2 * T, 3 * T
         o_slot, o_start, o_past, o_want = 4 * T, 4 * T + B, 4 * T + 2 * B + 1, 4 * T + 3 * B + 1
-        ids: List[int] = []
-        seq: List[int] = []
-        pos: List[int] = []
-        tslot: List[int] = []
-        starts = [0]
-        wants: List[int] = []
-        for b, (slot, past, tokens, want) in enumerate(seqs):
-            n = len(tokens)
-            ids.extend(tokens)
-            seq.extend([b] * n)
-            pos.extend(range(past, past + n))
-            tslot.extend([slot] * n)
-            wants.extend(starts[-1] + w for w in want)
-            starts.append(starts[-1] + n)
-        flat = (ids + seq + pos + tslot + [s[0] for s in seqs] + starts + [s[1] for s in seqs]
-                + wants)
-        total = len(flat)
-        h[:total] = torch.tensor(flat, dtype=torch.int32)
+        n_new = [len(s[2]) for s in seqs]
+        total = 4 * T + 3 * B + 1 + n_want
+        if T <= 64:
+            # a decode step or a few tokens: plain lists are quicker than array slices
+            ids: List[int] = []
+            seq: List[int] = []
+            pos: List[int] = []
+            tslot: List[int] = []
+            starts = [0]
+            wants: List[int] = []
+            for b, (slot, past, tokens, want) in enumerate(seqs):
+                n = n_new[b]
+                ids.extend(int(t) for t in tokens)
+                seq.extend([b] * n)
+                pos.extend(range(past, past + n))
+                tslot.extend([slot] * n)
+                wants.extend(starts[-1] + w for w in want)
+                starts.append(starts[-1] + n)
+            h[:total] = torch.tensor(ids + seq + pos + tslot + [s[0] for s in seqs] + starts
+                                     + [s[1] for s in seqs] + wants, dtype=torch.int32)
+        else:
+            starts = np.zeros(B + 1, dtype=np.int64)
+            np.cumsum(n_new, out=starts[1:])
+            flat = self.host_np[:total]
+            at = 0
+            for b, (slot, past, tokens, want) in enumerate(seqs):
+                n, lo = n_new[b], int(starts[b])
+                flat[o_ids + lo:o_ids + lo + n] = tokens
+                flat[o_seq + lo:o_seq + lo + n] = b
+                flat[o_pos + lo:o_pos + lo + n] = np.arange(past, past + n, dtype=np.int32)
+                flat[o_tslot + lo:o_tslot + lo + n] = slot
+                flat[o_slot + b] = slot
+                flat[o_past + b] = past
+                if len(want):
+                    flat[o_want + at:o_want + at + len(want)] = np.asarray(want, dtype=np.int64) + lo
+                    at += len(want)
+            flat[o_start:o_start + B + 1] = starts
         self.dev[:total].copy_(h[:total], non_blocking=True)
         self.copied.record()
         self.in_flight = True
         d = self.dev
-        new = [len(s[2]) for s in seqs]
+        new = n_new
         return StepContext(
             T=T, B=B, tok_ids=d[o_ids:o_ids + T], tok_seq=d[o_seq:o_seq + T],
             tok_pos=d[o_pos:o_pos + T], tok_slot=d[o_tslot:o_tslot + T],

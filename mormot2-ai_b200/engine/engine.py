@@ -13,6 +13,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from .. import kernels as K
@@ -137,13 +138,13 @@ class Engine:
             if e.slot in seen:
                 raise InferError(f"slot {e.slot} occurs twice in one step")
             seen.add(e.slot)
-            tokens = [int(t) for t in e.tokens]
-            if not tokens:
+            tokens = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+            if tokens.size == 0:
                 raise InferError(f"slot {e.slot}: a step of 0 tokens")
-            bad = [t for t in tokens if not 0 <= t < self.vocab_size]
-            if bad:
-                raise InferError(f"slot {e.slot}: token {bad[0]} is outside the vocabulary "
-                                 f"of {self.vocab_size}")
+            bad = (tokens < 0) | (tokens >= self.vocab_size)
+            if bad.any():
+                raise InferError(f"slot {e.slot}: token {int(tokens[bad][0])} is outside the "
+                                 f"vocabulary of {self.vocab_size}")
             want = [len(tokens) - 1] if e.want is None else [int(w) for w in e.want]
             if any(not 0 <= w < len(tokens) for w in want):
                 raise InferError(f"slot {e.slot}: wanted places {want} among {len(tokens)} tokens")
@@ -263,8 +264,8 @@ class Engine:
                 n = min(left, self.prefill_chunk, budget)
                 lo, hi = done[i], done[i] + n
                 w_here, d_here = [], []
-                for w in range(lo, hi):
-                    for r in row_of[i].get(w, ()):
+                for w in sorted(w for w in row_of[i] if lo <= w < hi):
+                    for r in row_of[i][w]:
                         w_here.append(w - lo)
                         d_here.append(r)
                 seqs.append((slot, past + lo, tokens[lo:hi], w_here))
