@@ -47,6 +47,7 @@ class StepBuffers:
         self.dev = torch.zeros(self.size, dtype=torch.int32, device=device)
         self.copied = torch.cuda.Event()
         self.in_flight = False
+        self.views = {}
 
     def fill(self, seqs: Sequence[Tuple[int, int, Sequence[int], Sequence[int]]]) -> StepContext:
         """``seqs = [(slot, past, tokens, want)]``; ``want`` are places among ``tokens``."""
@@ -56,7 +57,6 @@ class StepBuffers:
         assert 0 < T <= self.max_tokens and B <= self.max_seqs and n_want <= self.max_tokens
         if self.in_flight:
             self.copied.synchronize()  # the last copy must have read the host buffer
-        h = self.host
         o_ids, o_seq, o_pos, o_tslot = 0, T, 2 * T, 3 * T
         o_slot, o_start, o_past, o_want = 4 * T, 4 * T + B, 4 * T + 2 * B + 1, 4 * T + 3 * B + 1
         n_new = [len(s[2]) for s in seqs]
@@ -77,8 +77,8 @@ class StepBuffers:
                 tslot.extend([slot] * n)
                 wants.extend(starts[-1] + w for w in want)
                 starts.append(starts[-1] + n)
-            h[:total] = torch.tensor(ids + seq + pos + tslot + [s[0] for s in seqs] + starts
-                                     + [s[1] for s in seqs] + wants, dtype=torch.int32)
+            self.host_np[:total] = (ids + seq + pos + tslot + [s[0] for s in seqs] + starts
+                                    + [s[1] for s in seqs] + wants)
         else:
             starts = np.zeros(B + 1, dtype=np.int64)
             np.cumsum(n_new, out=starts[1:])
@@ -96,16 +96,21 @@ class StepBuffers:
                     flat[o_want + at:o_want + at + len(want)] = np.asarray(want, dtype=np.int64) + lo
                     at += len(want)
             flat[o_start:o_start + B + 1] = starts
-        self.dev[:total].copy_(h[:total], non_blocking=True)
+        self.dev[:total].copy_(self.host[:total], non_blocking=True)
         self.copied.record()
         self.in_flight = True
-        d = self.dev
-        new = n_new
+        # the device views depend on the counts only: made once per shape of step
+        views = self.views.get((T, B, n_want))
+        if views is None:
+            d = self.dev
+            views = (d[o_ids:o_ids + T], d[o_seq:o_seq + T], d[o_pos:o_pos + T],
+                     d[o_tslot:o_tslot + T], d[o_slot:o_slot + B], d[o_start:o_start + B + 1],
+                     d[o_past:o_past + B], d[o_want:o_want + n_want])
+            if len(self.views) < 4096:
+                self.views[(T, B, n_want)] = views
         return StepContext(
-            T=T, B=B, tok_ids=d[o_ids:o_ids + T], tok_seq=d[o_seq:o_seq + T],
-            tok_pos=d[o_pos:o_pos + T], tok_slot=d[o_tslot:o_tslot + T],
-            seq_slot=d[o_slot:o_slot + B],
-            seq_start=d[o_start:o_start + B + 1], seq_past=d[o_past:o_past + B],
-            want_rows=d[o_want:o_want + n_want], n_want=n_want, max_new=max(new),
-            max_len=max(s[1] + len(s[2]) for s in seqs), decode=all(n == 1 for n in new),
-            host_new=new, host_past=[s[1] for s in seqs], host_slots=[s[0] for s in seqs])
+            T=T, B=B, tok_ids=views[0], tok_seq=views[1], tok_pos=views[2], tok_slot=views[3],
+            seq_slot=views[4], seq_start=views[5], seq_past=views[6], want_rows=views[7],
+            n_want=n_want, max_new=max(n_new),
+            max_len=max(s[1] + len(s[2]) for s in seqs), decode=max(n_new) == 1,
+            host_new=n_new, host_past=[s[1] for s in seqs], host_slots=[s[0] for s in seqs])

@@ -138,13 +138,19 @@ class Engine:
             if e.slot in seen:
                 raise InferError(f"slot {e.slot} occurs twice in one step")
             seen.add(e.slot)
-            tokens = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
-            if tokens.size == 0:
-                raise InferError(f"slot {e.slot}: a step of 0 tokens")
-            bad = (tokens < 0) | (tokens >= self.vocab_size)
-            if bad.any():
-                raise InferError(f"slot {e.slot}: token {int(tokens[bad][0])} is outside the "
-                                 f"vocabulary of {self.vocab_size}")
+            if len(e.tokens) == 1:                      # a decode step: no arrays for one token
+                tokens = [int(e.tokens[0])]
+                if not 0 <= tokens[0] < self.vocab_size:
+                    raise InferError(f"slot {e.slot}: token {tokens[0]} is outside the "
+                                     f"vocabulary of {self.vocab_size}")
+            else:
+                tokens = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+                if tokens.size == 0:
+                    raise InferError(f"slot {e.slot}: a step of 0 tokens")
+                bad = (tokens < 0) | (tokens >= self.vocab_size)
+                if bad.any():
+                    raise InferError(f"slot {e.slot}: token {int(tokens[bad][0])} is outside "
+                                     f"the vocabulary of {self.vocab_size}")
             want = [len(tokens) - 1] if e.want is None else [int(w) for w in e.want]
             if any(not 0 <= w < len(tokens) for w in want):
                 raise InferError(f"slot {e.slot}: wanted places {want} among {len(tokens)} tokens")
@@ -243,6 +249,11 @@ class Engine:
         """Cuts a step into passes of at most ``prefill_chunk`` new tokens per sequence and
         ``max_step_tokens`` in all. Returns ``[(seqs, dest)]``: ``seqs`` as
         ``StepBuffers.fill`` takes them, ``dest`` the output rows of the pass's wanted logits."""
+        if (max(len(p[2]) for p in plan) <= self.prefill_chunk
+                and sum(len(p[2]) for p in plan) <= self.max_step_tokens):
+            # everything fits one pass (every decode step does): the plan is the pass, and its
+            # wanted rows come out in the order of the entries already
+            return [(plan, list(range(sum(len(p[3]) for p in plan))))]
         # output rows in the order of the entries and of their want
         row_of: List[Dict[int, List[int]]] = []
         at = 0
