@@ -1,7 +1,8 @@
 """Each part alone against the plain implementation's function of the same name, and the
 generality of putting parts together: a toy mixer with state of its own that is registered,
 built and stepped without a change to the library's files; an order of layers that names a
-layer twice; a layer that reads another layer's cache."""
+layer twice; a layer that reads another layer's cache; a toy feed-forward with routing and a toy
+position encoding, registered from here as well."""
 import math
 
 import numpy as np
@@ -312,3 +313,130 @@ def test_a_layer_twice_and_a_shared_cache(dtype):
                 [Run(0, None)], [Run(5, 0)]):
         with pytest.raises(ConfigError):
             DecoderModel(toy_spec(cfg, bad, ["attn", "attn"]))
+
+
+class TopOneExperts(Part):
+    """A toy feed-forward with routing, defined here, not in the library: a router picks one
+    of E small two-matrix experts per token (highest router logit, lowest index on a tie) and
+    the expert's output, weighted by the softmax probability of its logit, is added to x."""
+
+    def __init__(self, spec, prefix=""):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.inter, self.experts = p["hidden_size"], p["inter"], p["experts"]
+        self.base = prefix + "toy_moe."
+
+    def tensors(self):
+        e, h, i = self.experts, self.hidden, self.inter
+        return [TensorNeed(self.base + "router", (e, h)), TensorNeed(self.base + "w1", (e * i, h)),
+                TensorNeed(self.base + "w2", (e * h, i))]
+
+    def bind(self, weights, rt):
+        e, h, i = self.experts, self.hidden, self.inter
+        self.router = weights[self.base + "router"].float()
+        self.w1 = weights[self.base + "w1"].float().view(e, i, h)
+        self.w2 = weights[self.base + "w2"].float().view(e, h, i)
+
+    def forward(self, h, x, step):
+        hf = h.float()
+        logits = hf @ self.router.T                              # router logits in float32
+        prob = torch.softmax(logits, dim=-1)
+        pick = logits.argmax(dim=-1)
+        for e in range(self.experts):
+            rows = (pick == e).nonzero().flatten()
+            if rows.numel():
+                mid = torch.relu(hf[rows] @ self.w1[e].T)
+                x[rows] += prob[rows, e, None] * (mid @ self.w2[e].T)
+        return None
+
+
+class SlowedRope(Part):
+    """A toy position encoding, defined here: rotary over the first rot_dim values of a head
+    only, with every position counted as position / factor (the frequencies divided by it)."""
+
+    def __init__(self, spec, prefix=""):
+        super().__init__(spec, prefix)
+        self.theta, self.rot_dim = spec.params["theta"], spec.params["rot_dim"]
+        self.factor = spec.params["factor"]
+
+    def bind(self, weights, rt):
+        inv = plain.inverse_frequencies(self.theta, self.rot_dim) / np.float32(self.factor)
+        self.inv_freq = torch.from_numpy(inv.astype(np.float32)).to(rt.device)
+
+    def frequencies(self):
+        return self.inv_freq, self.rot_dim
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routed_feed_forward_and_toy_position_encoding(dtype):
+    """Two more kinds of parts from outside the library: layer 1's feed-forward routes each
+    token to one of three experts, and every attention rotates with a position encoding that
+    the library does not have (12 of 16 values of a head, positions slowed by 4)."""
+    from mormot2_ai_b200.parts import register_feed_forward, register_position
+    register_feed_forward("top_one_experts", TopOneExperts)
+    register_position("slowed_rope", SlowedRope)
+    cfg = Qwen3Config(vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=16, intermediate_size=96,
+                      max_position_embeddings=128, rms_norm_eps=1e-6, rope_theta=1e4,
+                      tie_word_embeddings=False)
+    base = cfg.to_model_spec()
+    moe = PartSpec("top_one_experts", {"hidden_size": 64, "inter": 40, "experts": 3})
+    layers = [base.layers[0],
+              LayerSpec(base.layers[1].block, base.layers[1].mixer, moe, base.layers[1].norms,
+                        base.layers[1].prefix)]
+    name = next(iter(base.positions))
+    positions = {name: PartSpec("slowed_rope", {"theta": 1e4, "rot_dim": 12, "factor": 4.0})}
+    spec = ModelSpec(base.architecture, base.vocab_size, base.hidden_size, base.max_positions,
+                     base.embedding, positions, tuple(layers), base.schedule, base.final_norm,
+                     base.head)
+    eng, w = build_engine(cfg, spec, dtype)
+
+    def reference(ids):
+        n, nh, nkv, hd, rot = len(ids), 4, 2, 16, 12
+        inv = plain.inverse_frequencies(1e4, rot) / np.float32(4.0)
+        cos, sin = plain.rotary_tables(inv.astype(np.float32), range(n))
+        x = plain.embed(w["model.embed_tokens.weight"], ids)
+        for li in range(2):
+            p = f"model.layers.{li}."
+            h = plain.rms_norm(x, w[p + "input_layernorm.weight"], 1e-6)
+            q = plain.linear(h, w[p + "self_attn.q_proj.weight"])
+            k = plain.linear(h, w[p + "self_attn.k_proj.weight"])
+            v = plain.linear(h, w[p + "self_attn.v_proj.weight"])
+            q = plain.rms_norm(q.reshape(n * nh, hd), w[p + "self_attn.q_norm.weight"], 1e-6)
+            k = plain.rms_norm(k.reshape(n * nkv, hd), w[p + "self_attn.k_norm.weight"], 1e-6)
+            q, k = q.reshape(n, nh, hd).copy(), k.reshape(n, nkv, hd).copy()
+            q[:, :, :rot] = plain.rope(q[:, :, :rot].reshape(n, nh * rot), nh, rot, cos,
+                                       sin).reshape(n, nh, rot)
+            k[:, :, :rot] = plain.rope(k[:, :, :rot].reshape(n, nkv * rot), nkv, rot, cos,
+                                       sin).reshape(n, nkv, rot)
+            a = plain.causal_attention(q.reshape(n, nh * hd), k.reshape(n, nkv * hd), v, nh, nkv,
+                                       hd, 0)
+            x = (x + plain.linear(a, w[p + "self_attn.o_proj.weight"])).astype(np.float32)
+            if li == 0:
+                x = plain.dense_block(x, w, p, cfg.to_dict())
+                continue
+            h = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-6).astype(np.float64)
+            logits = h @ w[p + "toy_moe.router"].astype(np.float64).T
+            prob = np.exp(logits - logits.max(1, keepdims=True))
+            prob /= prob.sum(1, keepdims=True)
+            out = np.zeros_like(h)
+            for t in range(n):
+                e = int(logits[t].argmax())
+                w1 = w[p + "toy_moe.w1"].reshape(3, 40, 64)[e].astype(np.float64)
+                w2 = w[p + "toy_moe.w2"].reshape(3, 64, 40)[e].astype(np.float64)
+                out[t] = prob[t, e] * (w2 @ np.maximum(w1 @ h[t], 0))
+            x = (x + out).astype(np.float32)
+        return plain.linear(plain.rms_norm(x, w["model.norm.weight"], 1e-6), w["lm_head.weight"])
+
+    rng = np.random.default_rng(4)
+    a, b = rng.integers(0, 300, 50).tolist(), rng.integers(0, 300, 23).tolist()
+    ra, rb = reference(a), reference(b)
+    s0, s1 = eng.open(), eng.open()
+    out = eng.step([Entry(s0, a[:40], [0, 39]), Entry(s1, b[:9])]).cpu().numpy()
+    ok, err = close(out, np.stack([ra[0], ra[39], rb[8]]), dtype)
+    assert ok, err
+    for t in range(10):
+        out = eng.step([Entry(s0, [a[40 + t]]), Entry(s1, [b[9 + t]])]).cpu().numpy()
+        ok, err = close(out, np.stack([ra[40 + t], rb[9 + t]]), dtype)
+        assert ok, (t, err)
+    eng.rt.check()
