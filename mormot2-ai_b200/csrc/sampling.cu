@@ -1,5 +1,5 @@
-// Choosing the next token on the device, one block per sequence: arg-max (greedy) and a draw
-// from softmax(logits / temperature).
+// Choosing the next token on the device: arg-max (greedy) and a draw from
+// softmax(logits / temperature), one block per sequence or, for wide rows, several.
 //
 // Semantics of the reference's sampler (paths within the reference project):
 //   arg-max   src/infer/mormot.ai.infer.sampler.pas:123-159 — the highest value, the lowest
@@ -208,6 +208,143 @@ sample_kernel(const float* __restrict__ logits, size_t stride, int V, double inv
   if (threadIdx.x == 0) out[blockIdx.x] = found >= 0 ? found : best.i;
 }
 
+// ---- the same draw by a cluster of SAMPLE_CTAS CTAs a row (wide vocabularies): each CTA takes
+// a contiguous share of the ids, the CTAs exchange their best value, their sum of weights and
+// the draw through each other's shared memory, and the CTA whose share holds the drawn point
+// walks it. Within a CTA every warp owns a contiguous run of ids and its lanes read it
+// interleaved (coalesced); the walk of the run that holds the point is a scan over 32 ids at a
+// time.
+#define SAMPLE_CTAS 8
+#define SAMPLE_CL_THREADS 512
+
+__device__ __forceinline__ uint32_t smp_smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ uint32_t smp_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void smp_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 8 bytes at `addr` (an address in this CTA's shared memory) as they lie in CTA `rank`
+__device__ __forceinline__ unsigned long long smp_peer_u64(uint32_t addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  unsigned long long v;
+  asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(SAMPLE_CL_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, size_t stride, int V, double inv_t,
+                      const int* __restrict__ state_index,
+                      unsigned long long* __restrict__ states, int* __restrict__ out) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  constexpr int WARPS = SAMPLE_CL_THREADS / 32;
+  __shared__ Best sh[32];
+  __shared__ double warp_sums[WARPS];
+  __shared__ __align__(8) unsigned long long mine_best;   // value bits << 32 | index
+  __shared__ __align__(8) double mine_sum;
+  __shared__ int found;
+  const int r = blockIdx.x / SAMPLE_CTAS;
+  const uint32_t rank = smp_cluster_rank();
+  const float* row = logits + r * stride;
+  const int share = (V + SAMPLE_CTAS - 1) / SAMPLE_CTAS;
+  const int lo = min(V, (int)rank * share), hi = min(V, lo + share);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // 1. the best finite-or-not value of the row: of this share, then of all shares
+  Best b = {0.f, -1};
+  if (hi > lo) {
+    b = block_argmax(row + lo, hi - lo, sh);
+    const float v = row[lo + b.i];
+    b = Best{v, v != v ? -1 : lo + b.i};  // an all-NaN share offers no candidate
+  }
+  if (threadIdx.x == 0)
+    mine_best = ((unsigned long long)__float_as_uint(b.v) << 32) | (unsigned)b.i;
+  smp_cluster_sync();
+  Best best = {0.f, -1};
+  for (uint32_t k = 0; k < SAMPLE_CTAS; ++k) {  // in share order: the lowest index wins a tie
+    const unsigned long long x = smp_peer_u64(smp_smem_u32(&mine_best), k);
+    const Best c = {__uint_as_float((unsigned)(x >> 32)), (int)(unsigned)x};
+    if (better(c, best)) best = c;
+  }
+  if (best.i < 0) best.i = 0;  // all NaN
+  const unsigned bits = __float_as_uint(best.v);
+  const bool no_draw = (bits & 0x7f800000u) == 0x7f800000u || best.i < 0;
+
+  // 2. the weights of this share: a contiguous run of ids per warp, lanes interleaved
+  const int per_warp = (hi - lo + WARPS - 1) / WARPS;
+  const int w0 = min(hi, lo + warp * per_warp), w1 = min(hi, w0 + per_warp);
+  double acc = 0.0;
+  if (!no_draw)
+    for (int i = w0 + lane; i < w1; i += 32) acc += weight_of(row[i], best.v, inv_t);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) warp_sums[warp] = acc;
+  if (threadIdx.x == 0) found = -1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < WARPS; ++w) t += warp_sums[w];  // in id order
+    mine_sum = t;
+  }
+  smp_cluster_sync();
+  double before = 0.0, total = 0.0;
+  for (uint32_t k = 0; k < SAMPLE_CTAS; ++k) {
+    const double v = __longlong_as_double((long long)smp_peer_u64(smp_smem_u32(&mine_sum), k));
+    if (k < rank) before += v;
+    total += v;
+  }
+  // 3. one splitmix64 draw of this sequence's stream: every CTA forms it from the state as it
+  // was, the first one stores the state that follows (after all have read it)
+  unsigned long long* st = states + state_index[r];
+  unsigned long long z = *st + 0x9E3779B97F4A7C15ull;
+  const unsigned long long next_state = z;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z = z ^ (z >> 31);
+  const double target = (double)(z >> 11) * (1.0 / 9007199254740992.0) * total;
+  smp_cluster_sync();
+  if (rank == 0 && threadIdx.x == 0) {
+    if (no_draw) out[r] = best.i;  // no finite best: nothing to draw from, the stream stays
+    else *st = next_state;
+  }
+  if (no_draw) return;
+  const double mine = mine_sum;
+  const bool last = rank == SAMPLE_CTAS - 1;
+  if (!(target >= before && (target < before + mine || last))) return;
+  // 4. the point lies in this share: the warp whose run holds it walks the run
+  double wb = before;
+  for (int w = 0; w < warp; ++w) wb += warp_sums[w];
+  const double ws = warp_sums[warp];
+  if (target >= wb && target < wb + ws) {
+    double cum = wb;
+    for (int i0 = w0; i0 < w1; i0 += 32) {
+      const int i = i0 + lane;
+      const double w = i < w1 ? weight_of(row[i], best.v, inv_t) : 0.0;
+      double incl = w;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const double v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      const unsigned hit = __ballot_sync(0xffffffffu, w > 0.0 && target < cum + incl);
+      if (hit) {
+        if (lane == 0) found = i0 + __ffs(hit) - 1;
+        break;
+      }
+      cum += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) out[r] = found >= 0 ? found : best.i;
+}
+
 // out[r] = a draw from softmax(logits[r] / temperature) with the splitmix64 state
 // states[state_index[r]], which advances by one draw.
 MB_EXPORT int mb_sample(const float* logits, long long stride, int rows, int V,
@@ -216,6 +353,12 @@ MB_EXPORT int mb_sample(const float* logits, long long stride, int rows, int V,
   if (rows <= 0) return 0;
   if (V <= 0) MB_FAIL("mb_sample: a vocabulary of %d", V);
   if (!(temperature >= 1e-30)) MB_FAIL("mb_sample: a temperature of %g is greedy", temperature);
+  if (V >= 16384 && rows <= 8192) {  // a wide row: a cluster of CTAs shares it
+    mb_launch_clusters(sample_cluster_kernel, dim3(rows * SAMPLE_CTAS), dim3(SAMPLE_CL_THREADS), 0,
+                       (cudaStream_t)stream, SAMPLE_CTAS, logits, (size_t)stride, V,
+                       1.0 / temperature, state_index, states, out);
+    MB_CHECK_LAUNCH("mb_sample");
+  }
   mb_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, 
       logits, (size_t)stride, V, 1.0 / temperature, state_index, states, out);
   MB_CHECK_LAUNCH("mb_sample");

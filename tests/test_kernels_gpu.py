@@ -440,6 +440,31 @@ def test_device_sampler_draws_what_the_plain_sampler_draws(settings):
     assert same == total
 
 
+def test_temperature_draw_over_a_wide_vocabulary():
+    """Wide rows are shared by a cluster of CTAs: the same draws as the plain sampler, with NaN,
+    infinities and ties in the row, a width that the CTAs do not share evenly, and a row without
+    any finite value (nothing is drawn and the stream does not move)."""
+    from mormot2_ai_b200.sampling import DeviceSampler, Sampling
+    V, rows, steps = 40003, 3, 12
+    g = torch.Generator().manual_seed(5)
+    sampler = DeviceSampler(torch.device(DEV), 4, V)
+    plain_samplers = [plain.PlainSampler(seed=7 + r, temperature=0.9) for r in range(rows)]
+    slots = torch.tensor([2, 0, 3], dtype=torch.int32, device=DEV)
+    for r in range(rows):
+        sampler.start(int(slots[r]), 7 + r)
+    for step in range(steps):
+        logits = torch.randn(rows, V, generator=g) * 3
+        logits[:, 20000] = logits[:, 20001]
+        logits[0, 5] = float("nan")
+        logits[1, 39999:] = float("-inf")
+        if step == 4:
+            logits[2, :] = float("-inf")
+            logits[2, 17] = float("nan")
+        got = sampler.pick(logits.to(DEV), slots, Sampling(temperature=0.9)).tolist()
+        want = [plain_samplers[r].next(logits[r].numpy()) for r in range(rows)]
+        assert got == want, step
+
+
 def test_vocab_limit_is_never_crossed():
     from mormot2_ai_b200.sampling import DeviceSampler, Sampling
     sampler = DeviceSampler(torch.device(DEV), 2, 64)
