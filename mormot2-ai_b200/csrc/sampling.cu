@@ -442,76 +442,18 @@ __device__ double block_walk(const double* __restrict__ w, int n, double target,
   return total;
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, double inv_t,
-                       int top_k, double top_p, double min_p,
-                       const int* __restrict__ state_index, unsigned long long* __restrict__ states,
-                       unsigned long long* __restrict__ scratch, size_t scratch_stride,
-                       int* __restrict__ out) {
-  mb_grid_wait();
-  mb_grid_launch_next();
-  __shared__ Best sh[32];
+// The end of a filtered draw, by one whole block: `n` candidate keys lie unsorted in `keys`.
+// They are sorted, cut by top-k, top-p and min-p in the reference's order, and one token is
+// drawn from what is left with the stream `state`; *result receives it.
+__device__ void filtered_finish(const float* __restrict__ row, const Best best, double inv_t,
+                                int top_k, double top_p, double min_p, double sum,
+                                unsigned long long* __restrict__ keys, size_t scratch_stride,
+                                int n, unsigned long long* __restrict__ state,
+                                int* __restrict__ result) {
   __shared__ double dsh[33];
   __shared__ int count_sh;
   __shared__ int result_sh;
   __shared__ double wsum[SAMPLE_THREADS];
-  const float* row = logits + blockIdx.x * stride;
-  unsigned long long* keys = scratch + blockIdx.x * scratch_stride;
-  const Best best = block_argmax(row, V, sh);
-  if ((__float_as_uint(best.v) & 0x7f800000u) == 0x7f800000u) {
-    if (threadIdx.x == 0) out[blockIdx.x] = best.i;
-    return;
-  }
-  // the sum of all weights (relative to the best one, which weighs 1) is needed only for a
-  // top-p over the whole vocabulary: p_i = w_i / sum
-  const bool whole_mass = top_p < 1.0 && top_k == 0;
-  double sum = 0.0;
-  if (whole_mass) {
-    double mine = 0.0;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) mine += weight_of(row[i], best.v, inv_t);
-    sum = block_sum_double(mine, dsh);
-  }
-  // A token is a candidate when its weight is at least t, tested on the exponent (no exp for
-  // the many that fail). The threshold goes down in small steps at first (each step is a pass
-  // over the row, but a step too far makes the sort below long), then in large ones.
-  double t = (top_k > 0 || top_p < 1.0) ? 1e-3 : min_p;
-  double log_t = t > 0.0 ? log(t) : -INFINITY;
-  int n = 0;
-  for (int round = 0;; ++round) {
-    int cnt = 0;
-    double above = 0.0;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float v = row[i];
-      const bool finite = (__float_as_uint(v) & 0x7f800000u) != 0x7f800000u;
-      const double x = ((double)v - (double)best.v) * inv_t;
-      if (finite && x >= log_t) {
-        ++cnt;
-        if (whole_mass) above += exp(x);
-      }
-    }
-    if (whole_mass) above = block_sum_double(above, dsh);
-    n = (int)(block_sum_double((double)cnt, dsh) + 0.5);
-    bool enough = true;
-    if (top_k > 0) enough = n >= top_k;
-    else if (top_p < 1.0) enough = above >= top_p * sum;
-    if (enough || t == 0.0) break;
-    t *= round < 6 ? 0.1 : 1e-3;
-    if (t < 1e-300) t = 0.0;
-    log_t = t > 0.0 ? log(t) : -INFINITY;
-  }
-  // gather the candidates' keys, pad to a power of two with the largest key
-  if (threadIdx.x == 0) count_sh = 0;
-  __syncthreads();
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
-    const bool finite = (__float_as_uint(v) & 0x7f800000u) != 0x7f800000u;
-    if (finite && ((double)v - (double)best.v) * inv_t >= log_t) {
-      const int at = atomicAdd(&count_sh, 1);
-      keys[at] = ((unsigned long long)(~ordered_bits(row[i])) << 32) | (unsigned)i;
-    }
-  }
-  __syncthreads();
-  n = count_sh;
   int np = 1;
   while (np < n) np <<= 1;
   for (int i = n + threadIdx.x; i < np; i += blockDim.x) keys[i] = ~0ull;
@@ -570,7 +512,7 @@ sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, d
     }
     const double kept = block_walk(wts, n, 0.0, false, true, wsum, &count_sh);
     if (threadIdx.x == 0) {
-      unsigned long long* st = states + state_index[blockIdx.x];
+      unsigned long long* st = state;
       unsigned long long z = (*st += 0x9E3779B97F4A7C15ull);
       z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
       z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
@@ -614,7 +556,7 @@ sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, d
     }
     double kept = 0.0;
     for (int c = 0; c < n; ++c) kept += w_of(c);
-    unsigned long long* st = states + state_index[blockIdx.x];
+    unsigned long long* st = state;
     unsigned long long z = (*st += 0x9E3779B97F4A7C15ull);
     z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
     z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
@@ -629,7 +571,202 @@ sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, d
     result_sh = pick;
   }
   __syncthreads();
-  if (threadIdx.x == 0) out[blockIdx.x] = result_sh;
+  if (threadIdx.x == 0) *result = result_sh;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, double inv_t,
+                       int top_k, double top_p, double min_p,
+                       const int* __restrict__ state_index, unsigned long long* __restrict__ states,
+                       unsigned long long* __restrict__ scratch, size_t scratch_stride,
+                       int* __restrict__ out) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  __shared__ Best sh[32];
+  __shared__ double dsh[33];
+  __shared__ int count_sh;
+  const float* row = logits + blockIdx.x * stride;
+  unsigned long long* keys = scratch + blockIdx.x * scratch_stride;
+  const Best best = block_argmax(row, V, sh);
+  if ((__float_as_uint(best.v) & 0x7f800000u) == 0x7f800000u) {
+    if (threadIdx.x == 0) out[blockIdx.x] = best.i;
+    return;
+  }
+  // the sum of all weights (relative to the best one, which weighs 1) is needed only for a
+  // top-p over the whole vocabulary: p_i = w_i / sum
+  const bool whole_mass = top_p < 1.0 && top_k == 0;
+  double sum = 0.0;
+  if (whole_mass) {
+    double mine = 0.0;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mine += weight_of(row[i], best.v, inv_t);
+    sum = block_sum_double(mine, dsh);
+  }
+  // A token is a candidate when its weight is at least t, tested on the exponent (no exp for
+  // the many that fail). The threshold goes down in small steps at first (each step is a pass
+  // over the row, but a step too far makes the sort below long), then in large ones.
+  double t = (top_k > 0 || top_p < 1.0) ? 1e-3 : min_p;
+  double log_t = t > 0.0 ? log(t) : -INFINITY;
+  int n = 0;
+  for (int round = 0;; ++round) {
+    int cnt = 0;
+    double above = 0.0;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = row[i];
+      const bool finite = (__float_as_uint(v) & 0x7f800000u) != 0x7f800000u;
+      const double x = ((double)v - (double)best.v) * inv_t;
+      if (finite && x >= log_t) {
+        ++cnt;
+        if (whole_mass) above += exp(x);
+      }
+    }
+    if (whole_mass) above = block_sum_double(above, dsh);
+    n = (int)(block_sum_double((double)cnt, dsh) + 0.5);
+    bool enough = true;
+    if (top_k > 0) enough = n >= top_k;
+    else if (top_p < 1.0) enough = above >= top_p * sum;
+    if (enough || t == 0.0) break;
+    t *= round < 6 ? 0.1 : 1e-3;
+    if (t < 1e-300) t = 0.0;
+    log_t = t > 0.0 ? log(t) : -INFINITY;
+  }
+  // gather the candidates' keys, pad to a power of two with the largest key
+  if (threadIdx.x == 0) count_sh = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    const bool finite = (__float_as_uint(v) & 0x7f800000u) != 0x7f800000u;
+    if (finite && ((double)v - (double)best.v) * inv_t >= log_t) {
+      const int at = atomicAdd(&count_sh, 1);
+      keys[at] = ((unsigned long long)(~ordered_bits(row[i])) << 32) | (unsigned)i;
+    }
+  }
+  __syncthreads();
+  n = count_sh;
+  filtered_finish(row, best, inv_t, top_k, top_p, min_p, sum, keys, scratch_stride, n,
+                  states + state_index[blockIdx.x], out + blockIdx.x);
+}
+
+// The filtered draw over a wide row: the passes over the vocabulary (best value, sum, counting
+// and gathering the candidates) are shared by a cluster of SAMPLE_CTAS CTAs that exchange their
+// counts and sums through each other's shared memory; the first CTA then sorts, filters and
+// draws as above. Every CTA takes the same decisions from the same exchanged numbers.
+__global__ void __launch_bounds__(SAMPLE_CL_THREADS)
+sample_filtered_cluster_kernel(const float* __restrict__ logits, size_t stride, int V,
+                               double inv_t, int top_k, double top_p, double min_p,
+                               const int* __restrict__ state_index,
+                               unsigned long long* __restrict__ states,
+                               unsigned long long* __restrict__ scratch, size_t scratch_stride,
+                               int* __restrict__ out) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  __shared__ Best sh[32];
+  __shared__ double dsh[33];
+  __shared__ __align__(8) unsigned long long mine_best;
+  __shared__ __align__(8) unsigned long long mail[2][2];  // [round parity][count, mass bits]
+  __shared__ int fill_sh;
+  const int r = blockIdx.x / SAMPLE_CTAS;
+  const uint32_t rank = smp_cluster_rank();
+  const float* row = logits + r * stride;
+  unsigned long long* keys = scratch + r * scratch_stride;
+  const int share = (V + SAMPLE_CTAS - 1) / SAMPLE_CTAS;
+  const int lo = min(V, (int)rank * share), hi = min(V, lo + share);
+
+  Best b = {0.f, -1};
+  if (hi > lo) {
+    b = block_argmax(row + lo, hi - lo, sh);
+    const float v = row[lo + b.i];
+    b = Best{v, v != v ? -1 : lo + b.i};
+  }
+  if (threadIdx.x == 0)
+    mine_best = ((unsigned long long)__float_as_uint(b.v) << 32) | (unsigned)b.i;
+  smp_cluster_sync();
+  Best best = {0.f, -1};
+  for (uint32_t k = 0; k < SAMPLE_CTAS; ++k) {
+    const unsigned long long x = smp_peer_u64(smp_smem_u32(&mine_best), k);
+    const Best c = {__uint_as_float((unsigned)(x >> 32)), (int)(unsigned)x};
+    if (better(c, best)) best = c;
+  }
+  if (best.i < 0) best.i = 0;  // all NaN
+  if ((__float_as_uint(best.v) & 0x7f800000u) == 0x7f800000u) {
+    if (rank == 0 && threadIdx.x == 0) out[r] = best.i;
+    smp_cluster_sync();  // no CTA leaves while another may still read its shared memory
+    return;              // the same for the whole cluster
+  }
+  // one exchange: every CTA leaves (count, mass) in the mailbox of this round's parity and
+  // reads all eight; the next round uses the other mailbox, so one barrier a round is enough
+  int round_no = 0;
+  int my_before = 0;  // candidates in the shares before this one (of the last exchange)
+  auto exchange = [&](int cnt, double mass, int& cnt_all, double& mass_all) {
+    const int par = round_no & 1;
+    ++round_no;
+    if (threadIdx.x == 0) {
+      mail[par][0] = (unsigned long long)(unsigned)cnt;
+      mail[par][1] = (unsigned long long)__double_as_longlong(mass);
+    }
+    smp_cluster_sync();
+    cnt_all = 0;
+    mass_all = 0.0;
+    my_before = 0;
+    for (uint32_t k = 0; k < SAMPLE_CTAS; ++k) {
+      const int c = (int)smp_peer_u64(smp_smem_u32(&mail[par][0]), k);
+      const double m = __longlong_as_double((long long)smp_peer_u64(smp_smem_u32(&mail[par][1]), k));
+      if (k < rank) my_before += c;
+      cnt_all += c;
+      mass_all += m;
+    }
+  };
+  const bool whole_mass = top_p < 1.0 && top_k == 0;
+  double sum = 0.0;
+  if (whole_mass) {
+    double mine = 0.0;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) mine += weight_of(row[i], best.v, inv_t);
+    mine = block_sum_double(mine, dsh);
+    int unused;
+    exchange(0, mine, unused, sum);
+  }
+  double t = (top_k > 0 || top_p < 1.0) ? 1e-3 : min_p;
+  double log_t = t > 0.0 ? log(t) : -INFINITY;
+  int n = 0;
+  for (int round = 0;; ++round) {
+    int cnt = 0;
+    double above = 0.0;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const float v = row[i];
+      const bool finite = (__float_as_uint(v) & 0x7f800000u) != 0x7f800000u;
+      const double x = ((double)v - (double)best.v) * inv_t;
+      if (finite && x >= log_t) {
+        ++cnt;
+        if (whole_mass) above += exp(x);
+      }
+    }
+    if (whole_mass) above = block_sum_double(above, dsh);
+    cnt = (int)(block_sum_double((double)cnt, dsh) + 0.5);
+    double above_all;
+    exchange(cnt, above, n, above_all);
+    bool enough = true;
+    if (top_k > 0) enough = n >= top_k;
+    else if (top_p < 1.0) enough = above_all >= top_p * sum;
+    if (enough || t == 0.0) break;
+    t *= round < 6 ? 0.1 : 1e-3;
+    if (t < 1e-300) t = 0.0;
+    log_t = t > 0.0 ? log(t) : -INFINITY;
+  }
+  // every share's candidates go behind those of the shares before it
+  if (threadIdx.x == 0) fill_sh = 0;
+  __syncthreads();
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = row[i];
+    const bool finite = (__float_as_uint(v) & 0x7f800000u) != 0x7f800000u;
+    if (finite && ((double)v - (double)best.v) * inv_t >= log_t) {
+      const int at = my_before + atomicAdd(&fill_sh, 1);
+      keys[at] = ((unsigned long long)(~ordered_bits(v)) << 32) | (unsigned)i;
+    }
+  }
+  __threadfence();
+  smp_cluster_sync();  // all keys are written (and nobody reads a mailbox any more)
+  if (rank != 0) return;
+  filtered_finish(row, best, inv_t, top_k, top_p, min_p, sum, keys, scratch_stride, n,
+                  states + state_index[r], out + r);
 }
 
 // Like mb_sample, with top_k (0: off), top_p (1: off) and min_p (0: off). `scratch`:
@@ -646,6 +783,13 @@ MB_EXPORT int mb_sample_filtered(const float* logits, long long stride, int rows
     MB_FAIL("mb_sample_filtered: top_k %d, top_p %g, min_p %g", top_k, top_p, min_p);
   if (scratch_stride < V || (scratch_stride & (scratch_stride - 1)))
     MB_FAIL("mb_sample_filtered: a scratch row of %lld words for %d tokens", scratch_stride, V);
+  if (V >= 16384 && rows <= 8192) {  // a wide row: a cluster of CTAs shares the passes over it
+    mb_launch_clusters(sample_filtered_cluster_kernel, dim3(rows * SAMPLE_CTAS),
+                       dim3(SAMPLE_CL_THREADS), 0, (cudaStream_t)stream, SAMPLE_CTAS, logits,
+                       (size_t)stride, V, 1.0 / temperature, top_k, top_p, min_p, state_index,
+                       states, scratch, (size_t)scratch_stride, out);
+    MB_CHECK_LAUNCH("mb_sample_filtered");
+  }
   mb_launch(sample_filtered_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, 
       logits, (size_t)stride, V, 1.0 / temperature, top_k, top_p, min_p, state_index, states,
       scratch, (size_t)scratch_stride, out);

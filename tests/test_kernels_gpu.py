@@ -440,7 +440,11 @@ def test_device_sampler_draws_what_the_plain_sampler_draws(settings):
     assert same == total
 
 
-def test_temperature_draw_over_a_wide_vocabulary():
+@pytest.mark.parametrize("settings", [dict(temperature=0.9), dict(temperature=1.0, top_k=7),
+                                      dict(temperature=0.8, top_p=0.85),
+                                      dict(temperature=1.2, min_p=0.03),
+                                      dict(temperature=0.8, top_k=50, top_p=0.9, min_p=0.01)])
+def test_draws_over_a_wide_vocabulary(settings):
     """Wide rows are shared by a cluster of CTAs: the same draws as the plain sampler, with NaN,
     infinities and ties in the row, a width that the CTAs do not share evenly, and a row without
     any finite value (nothing is drawn and the stream does not move)."""
@@ -448,7 +452,7 @@ def test_temperature_draw_over_a_wide_vocabulary():
     V, rows, steps = 40003, 3, 12
     g = torch.Generator().manual_seed(5)
     sampler = DeviceSampler(torch.device(DEV), 4, V)
-    plain_samplers = [plain.PlainSampler(seed=7 + r, temperature=0.9) for r in range(rows)]
+    plain_samplers = [plain.PlainSampler(seed=7 + r, **settings) for r in range(rows)]
     slots = torch.tensor([2, 0, 3], dtype=torch.int32, device=DEV)
     for r in range(rows):
         sampler.start(int(slots[r]), 7 + r)
@@ -460,7 +464,7 @@ def test_temperature_draw_over_a_wide_vocabulary():
         if step == 4:
             logits[2, :] = float("-inf")
             logits[2, 17] = float("nan")
-        got = sampler.pick(logits.to(DEV), slots, Sampling(temperature=0.9)).tolist()
+        got = sampler.pick(logits.to(DEV), slots, Sampling(**settings)).tolist()
         want = [plain_samplers[r].next(logits[r].numpy()) for r in range(rows)]
         assert got == want, step
 
