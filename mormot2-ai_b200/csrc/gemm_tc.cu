@@ -425,6 +425,34 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (n0 + c0 >= N) break;
         float v[16];
         tmem_ld16(taddr + c0, v);
+        // adding into the float32 residual: a whole 128-byte line of the row (32 columns) is
+        // asked for together, and the next line is brought near while this one is added. The
+        // condition is the same for the whole warp (the loads from tensor memory are
+        // warp-wide instructions); only the memory accesses depend on the thread's row.
+        if (mode == TC_ADD && c_dtype == MB_F32 && c0 + 32 <= BN && n0 + c0 + 32 <= N &&
+            (ldc & 3) == 0 && ((uintptr_t)C & 15) == 0) {
+          float v2[16];
+          tmem_ld16(taddr + c0 + 16, v2);
+          if (a < M) {
+            float4* p = (float4*)((float*)C + (size_t)a * ldc + n0 + c0);
+            if (c0 + 64 <= BN && n0 + c0 + 64 <= N)
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(p + 8));
+            float4 r[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) r[j] = p[j];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              r[j].x += v[4 * j]; r[j].y += v[4 * j + 1];
+              r[j].z += v[4 * j + 2]; r[j].w += v[4 * j + 3];
+              r[4 + j].x += v2[4 * j]; r[4 + j].y += v2[4 * j + 1];
+              r[4 + j].z += v2[4 * j + 2]; r[4 + j].w += v2[4 * j + 3];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) p[j] = r[j];
+          }
+          c0 += 16;  // two steps of columns done
+          continue;
+        }
         if (a < M)
           store_row16(v, C, c_dtype, ldc, a, n0 + c0, N, mode, part, partial_ld, partial_stride);
       }
