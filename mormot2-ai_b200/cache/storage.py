@@ -9,7 +9,7 @@ path); the reference keeps half floats or floats (``model.qwen3.cuda.pas:907-937
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 

@@ -10,7 +10,7 @@ import json
 import math
 import os
 from dataclasses import dataclass
-from typing import Any, Dict, Optional, Tuple
+from typing import Any, Dict, Tuple
 
 from ..errors import ConfigError
 from .spec import LayerSpec, ModelSpec, PartSpec, Run

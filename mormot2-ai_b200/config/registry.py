@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Any, Dict, List, Type
+from typing import Any, Dict, List
 
 from ..errors import ConfigError
 

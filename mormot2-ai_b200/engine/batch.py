@@ -8,7 +8,7 @@ device buffer that is filled by one copy from pinned host memory.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Sequence, Tuple
 
 import numpy as np
 import torch

@@ -14,7 +14,7 @@ The loop decides on the host and computes nothing: it drives a *stepper* (``open
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Iterable, List, Optional, Sequence, Set, Tuple
+from typing import Dict, List, Optional, Sequence, Set, Tuple
 
 from ..cache.pages import pages_for
 from ..errors import InferError

@@ -7,7 +7,7 @@ layers, the final norm over the rows whose logits are wanted, the head).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional
 
 import torch
 

@@ -6,7 +6,7 @@ head h reads KV head h div (heads div kv_heads) (``backend.cpu.pas:1253``).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 import torch
 

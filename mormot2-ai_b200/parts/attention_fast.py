@@ -2,7 +2,6 @@
 kernel takes a call, and how a sequence's pages are shared out over CTAs."""
 from __future__ import annotations
 
-from typing import Tuple
 
 import torch
 

@@ -3,7 +3,7 @@ top-k / top-p / min-p filters as kernels (``csrc/sampling.cu``). Only the chosen
 come back to the host."""
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional
 
 import torch
 

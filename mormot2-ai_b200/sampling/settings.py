@@ -7,7 +7,6 @@ import json
 import math
 import os
 from dataclasses import dataclass, replace
-from typing import Any, Dict, Optional
 
 from ..errors import InferError
 

@@ -11,7 +11,7 @@ reference refuses it (``decoder.pas:1950-1957``).
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, List
+from typing import Dict, Iterable
 
 import torch
 

@@ -12,7 +12,7 @@ from __future__ import annotations
 import json
 import os
 import struct
-from typing import Dict, Iterable, List, Mapping, Tuple
+from typing import Dict, List, Mapping, Tuple
 
 import numpy as np
 import torch

@@ -12,8 +12,8 @@ import torch
 from mormot2_ai_b200 import (ConfigError, DecoderModel, Engine, Entry, LayerSpec, ModelSpec,
                              PartSpec, Qwen3Config, Run, Runtime)
 from mormot2_ai_b200.parts.block import settle
-from mormot2_ai_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Part,
-                                   StateNeed, TensorNeed, register_mixer)
+from mormot2_ai_b200.parts import (FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Part, StateNeed,
+                                   TensorNeed, register_mixer)
 from mormot2_ai_b200.weights import random_tensors
 from tests.conftest import close, tiny_b
 from tests.gpu_helpers import DEV, make_line, make_step
