@@ -240,7 +240,7 @@ static MbEncodeTiled mb_encode_tiled() {
 // A map over a row-major bfloat16 matrix [rows, cols] with `ld` elements from row to row,
 // tiles of box_rows x 64 columns, 128-byte swizzle, zeros outside. Returns false with a
 // message in g_mb_error if the matrix cannot be mapped (alignment).
-static bool mb_make_map_bf16(CUtensorMap* map, const void* base, long long rows, long long cols,
+__attribute__((unused)) static bool mb_make_map_bf16(CUtensorMap* map, const void* base, long long rows, long long cols,
                              long long ld, int box_rows, const char* what) {
   MbEncodeTiled enc = mb_encode_tiled();
   if (!enc) {
