@@ -81,7 +81,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
 
 // The same for rows of 4 * RMS_THREADS * VEC values at most (a multiple of 4): the row is read
 // once with 16-byte loads, kept in registers, and written with 8- or 16-byte stores.
-template <typename TO, int VEC, int RMS_THREADS>
+template <typename TO, int VEC, int RMS_THREADS, bool PARTIAL>
 __global__ void __launch_bounds__(RMS_THREADS)
 rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partial, int parts,
                    size_t part_stride, const void* __restrict__ w, int w_bf16, float eps,
@@ -99,7 +99,7 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partial, int
     const int c = (i * RMS_THREADS + threadIdx.x) * 4;
     v[i] = c < H ? *(const float4*)(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  if (parts > 0) {
+  if (PARTIAL) {  // a kernel of its own: the loads in flight below cost registers
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const int c = (i * RMS_THREADS + threadIdx.x) * 4;
@@ -165,18 +165,22 @@ static int rmsnorm_launch(float* x, const float* partial, int parts, size_t part
     // loads; many rows: 256 threads a row and more rows per SM
     const int w_bf16 = sizeof(TW) == 2;
 #define RMS_GO(V_, T_)                                                                      \
-  mb_launch(rmsnorm_vec_kernel<TO, V_, T_>, dim3(R), dim3(T_), 0, s, x, partial, parts,     \
-            part_stride, w, w_bf16, eps, (TO*)y, rows, H)
+  if (parts > 0)                                                                            \
+    mb_launch(rmsnorm_vec_kernel<TO, V_, T_, true>, dim3(R), dim3(T_), 0, s, x, partial,    \
+              parts, part_stride, w, w_bf16, eps, (TO*)y, rows, H);                         \
+  else                                                                                      \
+    mb_launch(rmsnorm_vec_kernel<TO, V_, T_, false>, dim3(R), dim3(T_), 0, s, x, partial,   \
+              parts, part_stride, w, w_bf16, eps, (TO*)y, rows, H)
     if ((R <= 256 && H > 1024) || H > 4 * 256 * 4) {
       const int vec = (H + 4 * 1024 - 1) / (4 * 1024);
-      if (vec <= 1) RMS_GO(1, 1024);
-      else if (vec <= 2) RMS_GO(2, 1024);
-      else RMS_GO(4, 1024);
+      if (vec <= 1) { RMS_GO(1, 1024); }
+      else if (vec <= 2) { RMS_GO(2, 1024); }
+      else { RMS_GO(4, 1024); }
     } else {
       const int vec = (H + 4 * 256 - 1) / (4 * 256);
-      if (vec <= 1) RMS_GO(1, 256);
-      else if (vec <= 2) RMS_GO(2, 256);
-      else RMS_GO(4, 256);
+      if (vec <= 1) { RMS_GO(1, 256); }
+      else if (vec <= 2) { RMS_GO(2, 256); }
+      else { RMS_GO(4, 256); }
     }
 #undef RMS_GO
     MB_CHECK_LAUNCH("mb_rmsnorm");
