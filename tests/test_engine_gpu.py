@@ -208,7 +208,8 @@ def test_padding_and_batch_mates_change_nothing(tiny_b_model):
     assert np.abs(out[1:10] - alone).max() <= 2e-6
 
 
-def test_layers_of_full_size_bfloat16_against_float32():
+@pytest.mark.parametrize("lens", [(1100, 200), (4200,)], ids=["two_prompts", "long_prompt"])
+def test_layers_of_full_size_bfloat16_against_float32(lens):
     """Two layers with the sizes of a real model (width 4096, 32 heads of 128 on 8, feed-forward
     12288, vocabulary 151936): the tensor-core path (products on CTA pairs for the prompts, the
     decode forms with split K, both tensor-core attention kernels) against the engine's own
@@ -218,17 +219,17 @@ def test_layers_of_full_size_bfloat16_against_float32():
         "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "vocab_size": 151936,
         "hidden_size": 4096, "intermediate_size": 12288, "num_hidden_layers": 2,
         "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
-        "max_position_embeddings": 4096, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+        "max_position_embeddings": 8192, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
         "tie_word_embeddings": False, "hidden_act": "silu", "attention_bias": False})
     from mormot2_ai_b200 import DecoderModel, Runtime
     from mormot2_ai_b200.weights.random_init import random_tensors
     names = DecoderModel(cfg.to_model_spec()).tensors()
     weights = random_tensors(names, 5, 0.03, 0.1, torch.bfloat16, "cuda:0")   # one set for both
-    kw = dict(max_tokens=4096, max_context=2048, max_slots=4)
+    kw = dict(max_tokens=8192, max_context=4608, max_slots=4)
     fast = Engine(cfg, weights, Runtime(torch.bfloat16), **kw)
     slow = Engine(cfg, weights, Runtime(torch.float32), **kw)
     g = torch.Generator().manual_seed(3)
-    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (1100, 200)]
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
 
     def rel(a, b):
         return float((a - b).abs().max() / b.abs().max())
@@ -241,7 +242,8 @@ def test_layers_of_full_size_bfloat16_against_float32():
     assert float(b.abs().max()) > 0.5                      # logits of a size that means something
     assert rel(a, b) <= 3e-2, rel(a, b)
     for step in range(3):                                   # decode: the token the 32-bit path picks
-        tokens = b[[2, 5]].argmax(dim=1).tolist() if step == 0 else b.argmax(dim=1).tolist()
+        last = [3 * i + 2 for i in range(len(prompts))]     # each prompt's last wanted row
+        tokens = b[last].argmax(dim=1).tolist() if step == 0 else b.argmax(dim=1).tolist()
         a = fast.step([Entry(s, [t]) for s, t in zip(slots_f, tokens)])
         b = slow.step([Entry(s, [t]) for s, t in zip(slots_s, tokens)])
         assert rel(a, b) <= 3e-2, (step, rel(a, b))
