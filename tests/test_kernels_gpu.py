@@ -74,15 +74,19 @@ def test_rmsnorm_many_rows(H):
     assert rel(out.float().cpu(), plain.rms_norm(total.numpy(), w.float().numpy(), 1e-6)) <= 8e-3
 
 
-def test_rmsnorm_adds_split_partials():
+@pytest.mark.parametrize("H,n_parts", [(320, 3), (2048, 9), (4096, 8), (5120, 1)])
+def test_rmsnorm_adds_split_partials(H, n_parts):
+    """Few rows, as a decode step has them: narrow and wide rows, up to nine partial sums."""
     g = torch.Generator().manual_seed(1)
-    x = torch.randn(5, 320, generator=g)
-    parts = torch.randn(3, 5, 320, generator=g)
-    w = 1 + 0.1 * torch.randn(320, generator=g)
+    x = torch.randn(5, H, generator=g)
+    parts = torch.randn(n_parts, 5, H, generator=g)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
     xd = x.to(DEV)
-    out = torch.empty(5, 320, device=DEV)
+    out = torch.empty(5, H, device=DEV)
     K.rmsnorm(xd, w.to(DEV), 1e-6, out, partial=parts.to(DEV))
-    total = ((x + parts[0]) + parts[1]) + parts[2]            # in split order
+    total = x.clone()
+    for p in parts:                                            # in split order
+        total = total + p
     assert torch.equal(xd.cpu(), total)
     assert rel(out.cpu(), plain.rms_norm(total.numpy(), w.numpy(), 1e-6)) <= 2e-6
 
