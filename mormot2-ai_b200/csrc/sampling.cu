@@ -442,6 +442,52 @@ __device__ double block_walk(const double* __restrict__ w, int n, double target,
   return total;
 }
 
+// The search for the candidates' threshold (on the exponent: log of the weight relative to the
+// best). It starts at log(1e-3) and goes down until the candidates are enough for the filters
+// (k of them, or top_p of the mass); if they are far more than needed (a flat distribution) it
+// goes up again by bisection between a threshold that gave enough and one that did not, since
+// the sort that follows grows with their number. It ends right after a pass at the threshold it
+// keeps. `may_raise` is off when the threshold itself is the filter (min-p alone).
+struct ThreshSearch {
+  double log_t, ok, bad;
+  bool have_ok, finish_next;
+};
+__device__ __forceinline__ void thresh_start(ThreshSearch& s, double t) {
+  s.log_t = t > 0.0 ? log(t) : -INFINITY;
+  s.ok = 0.0;
+  s.bad = 0.0;  // a threshold above the best weight keeps nothing
+  s.have_ok = false;
+  s.finish_next = false;
+}
+// after a pass at s.log_t that found n candidates (enough or not): true when the search is over
+__device__ __forceinline__ bool thresh_step(ThreshSearch& s, bool enough, int n, int cap,
+                                            int round, bool may_raise) {
+  if (enough) {
+    if (!may_raise || s.finish_next || n <= cap || round >= 20) return true;
+    s.ok = s.log_t;
+    s.have_ok = true;
+    const double mid = 0.5 * (s.ok + s.bad);
+    if (!(mid > s.ok && mid < s.bad)) return true;
+    s.log_t = mid;
+    return false;
+  }
+  if (s.log_t == -INFINITY) return true;  // every finite token is a candidate already
+  s.bad = s.log_t;
+  if (!s.have_ok) {  // still on the way down
+    s.log_t += round < 6 ? -2.302585092994046 : -6.907755278982137;
+    if (s.log_t < -690.0) s.log_t = -INFINITY;
+    return false;
+  }
+  const double mid = 0.5 * (s.ok + s.bad);
+  if (round >= 20 || !(mid > s.ok && mid < s.bad)) {
+    s.log_t = s.ok;  // one more pass at the threshold that is known to be enough
+    s.finish_next = true;
+  } else {
+    s.log_t = mid;
+  }
+  return false;
+}
+
 // The end of a filtered draw, by one whole block: `n` candidate keys lie unsorted in `keys`.
 // They are sorted, cut by top-k, top-p and min-p in the reference's order, and one token is
 // drawn from what is left with the stream `state`; *result receives it.
@@ -601,13 +647,15 @@ sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, d
     for (int i = threadIdx.x; i < V; i += blockDim.x) mine += weight_of(row[i], best.v, inv_t);
     sum = block_sum_double(mine, dsh);
   }
-  // A token is a candidate when its weight is at least t, tested on the exponent (no exp for
-  // the many that fail). The threshold goes down in small steps at first (each step is a pass
-  // over the row, but a step too far makes the sort below long), then in large ones.
-  double t = (top_k > 0 || top_p < 1.0) ? 1e-3 : min_p;
-  double log_t = t > 0.0 ? log(t) : -INFINITY;
+  // A token is a candidate when its weight is at least the threshold, tested on the exponent
+  // (no exp for the many that fail).
+  ThreshSearch ts;
+  thresh_start(ts, (top_k > 0 || top_p < 1.0) ? 1e-3 : min_p);
+  const bool may_raise = top_k > 0 || top_p < 1.0;
+  const int cap = top_k > 0 ? max(2 * top_k, 1024) : 4096;
   int n = 0;
   for (int round = 0;; ++round) {
+    const double log_t = ts.log_t;
     int cnt = 0;
     double above = 0.0;
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
@@ -624,11 +672,9 @@ sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, d
     bool enough = true;
     if (top_k > 0) enough = n >= top_k;
     else if (top_p < 1.0) enough = above >= top_p * sum;
-    if (enough || t == 0.0) break;
-    t *= round < 6 ? 0.1 : 1e-3;
-    if (t < 1e-300) t = 0.0;
-    log_t = t > 0.0 ? log(t) : -INFINITY;
+    if (thresh_step(ts, enough, n, cap, round, may_raise)) break;
   }
+  const double log_t = ts.log_t;
   // gather the candidates' keys, pad to a power of two with the largest key
   if (threadIdx.x == 0) count_sh = 0;
   __syncthreads();
@@ -724,10 +770,13 @@ sample_filtered_cluster_kernel(const float* __restrict__ logits, size_t stride, 
     int unused;
     exchange(0, mine, unused, sum);
   }
-  double t = (top_k > 0 || top_p < 1.0) ? 1e-3 : min_p;
-  double log_t = t > 0.0 ? log(t) : -INFINITY;
+  ThreshSearch ts;
+  thresh_start(ts, (top_k > 0 || top_p < 1.0) ? 1e-3 : min_p);
+  const bool may_raise = top_k > 0 || top_p < 1.0;
+  const int cap = top_k > 0 ? max(2 * top_k, 1024) : 4096;
   int n = 0;
   for (int round = 0;; ++round) {
+    const double log_t = ts.log_t;
     int cnt = 0;
     double above = 0.0;
     for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
@@ -746,11 +795,9 @@ sample_filtered_cluster_kernel(const float* __restrict__ logits, size_t stride, 
     bool enough = true;
     if (top_k > 0) enough = n >= top_k;
     else if (top_p < 1.0) enough = above_all >= top_p * sum;
-    if (enough || t == 0.0) break;
-    t *= round < 6 ? 0.1 : 1e-3;
-    if (t < 1e-300) t = 0.0;
-    log_t = t > 0.0 ? log(t) : -INFINITY;
+    if (thresh_step(ts, enough, n, cap, round, may_raise)) break;
   }
+  const double log_t = ts.log_t;
   // every share's candidates go behind those of the shares before it
   if (threadIdx.x == 0) fill_sh = 0;
   __syncthreads();
