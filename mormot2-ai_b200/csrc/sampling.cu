@@ -15,6 +15,7 @@
 MB_DEFINE_LAST_ERROR
 
 #define SAMPLE_THREADS 1024
+#define SORT_CHUNK 2048  // keys that are sorted in shared memory at a time (16 KB)
 
 struct Best {
   float v;
@@ -488,9 +489,74 @@ __device__ __forceinline__ bool thresh_step(ThreshSearch& s, bool enough, int n,
   return false;
 }
 
-// The end of a filtered draw, by one whole block: `n` candidate keys lie unsorted in `keys`.
-// They are sorted, cut by top-k, top-p and min-p in the reference's order, and one token is
-// drawn from what is left with the stream `state`; *result receives it.
+// The n candidate keys in `keys` sorted ascending (padded to the next power of two with the
+// largest key), by one block (PARTS = 1) or by the PARTS CTAs of a cluster, of which this is
+// number `part`: every CTA takes every PARTS-th chunk and a PARTS-th of each far step, and they
+// meet at the cluster's barrier after each step. Bitonic: steps whose partners lie within
+// SORT_CHUNK keys of each other run in shared memory, a chunk at a time and as many steps in a
+// row as stay inside the chunk; only the far steps of the upper levels go through global memory.
+template <int PARTS>
+__device__ void sort_candidates(unsigned long long* __restrict__ keys, int n, int part) {
+  __shared__ unsigned long long chunk[SORT_CHUNK];
+  auto meet = [&]() {
+    if (PARTS == 1) {
+      __syncthreads();
+    } else {
+      __threadfence();
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+  };
+  int np = 1;
+  while (np < n) np <<= 1;
+  for (int i = n + part * blockDim.x + threadIdx.x; i < np; i += PARTS * blockDim.x)
+    keys[i] = ~0ull;
+  meet();
+  const int cn = np < SORT_CHUNK ? np : SORT_CHUNK;
+  // levels k_lo .. k_hi of chunk-local steps (all steps of a level when k <= cn, else the last
+  // ones, j <= cn / 2) for this CTA's chunks
+  auto local_levels = [&](int k_lo, int k_hi) {
+    for (int base = part * cn; base < np; base += PARTS * cn) {
+      for (int i = threadIdx.x; i < cn; i += blockDim.x) chunk[i] = keys[base + i];
+      __syncthreads();
+      for (int k = k_lo; k <= k_hi; k <<= 1) {
+        for (int j = (k >> 1) < cn ? (k >> 1) : (cn >> 1); j > 0; j >>= 1) {
+          for (int i = threadIdx.x; i < cn; i += blockDim.x) {
+            const int l = i ^ j;
+            if (l > i) {
+              const unsigned long long a = chunk[i], b = chunk[l];
+              const bool up = ((base + i) & k) == 0;
+              if ((a > b) == up) { chunk[i] = b; chunk[l] = a; }
+            }
+          }
+          __syncthreads();
+        }
+      }
+      for (int i = threadIdx.x; i < cn; i += blockDim.x) keys[base + i] = chunk[i];
+      __syncthreads();
+    }
+    meet();
+  };
+  local_levels(2, cn);
+  for (int k = 2 * cn; k <= np; k <<= 1) {
+    for (int j = k >> 1; j >= cn; j >>= 1) {
+      for (int i = part * blockDim.x + threadIdx.x; i < np; i += PARTS * blockDim.x) {
+        const int l = i ^ j;
+        if (l > i) {
+          const unsigned long long a = keys[i], b = keys[l];
+          const bool up = (i & k) == 0;
+          if ((a > b) == up) { keys[i] = b; keys[l] = a; }
+        }
+      }
+      meet();
+    }
+    local_levels(k, k);
+  }
+}
+
+// The end of a filtered draw, by one whole block: `n` candidate keys lie sorted in `keys`. They
+// are cut by top-k, top-p and min-p in the reference's order, and one token is drawn from what
+// is left with the stream `state`; *result receives it.
 __device__ void filtered_finish(const float* __restrict__ row, const Best best, double inv_t,
                                 int top_k, double top_p, double min_p, double sum,
                                 unsigned long long* __restrict__ keys, size_t scratch_stride,
@@ -502,22 +568,6 @@ __device__ void filtered_finish(const float* __restrict__ row, const Best best, 
   __shared__ double wsum[SAMPLE_THREADS];
   int np = 1;
   while (np < n) np <<= 1;
-  for (int i = n + threadIdx.x; i < np; i += blockDim.x) keys[i] = ~0ull;
-  __syncthreads();
-  // bitonic sort, ascending
-  for (int k = 2; k <= np; k <<= 1) {
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int i = threadIdx.x; i < np; i += blockDim.x) {
-        const int l = i ^ j;
-        if (l > i) {
-          const unsigned long long a = keys[i], b = keys[l];
-          const bool up = (i & k) == 0;
-          if ((a > b) == up) { keys[i] = b; keys[l] = a; }
-        }
-      }
-      __syncthreads();
-    }
-  }
   // The candidates' weights in sorted order, once, next to the keys (there is room unless more
   // than half of the vocabulary is a candidate: then one thread walks them as they are).
   double* wts = 2 * (size_t)np <= scratch_stride ? (double*)(keys + np) : nullptr;
@@ -688,6 +738,7 @@ sample_filtered_kernel(const float* __restrict__ logits, size_t stride, int V, d
   }
   __syncthreads();
   n = count_sh;
+  sort_candidates<1>(keys, n, 0);
   filtered_finish(row, best, inv_t, top_k, top_p, min_p, sum, keys, scratch_stride, n,
                   states + state_index[blockIdx.x], out + blockIdx.x);
 }
@@ -811,6 +862,7 @@ sample_filtered_cluster_kernel(const float* __restrict__ logits, size_t stride, 
   }
   __threadfence();
   smp_cluster_sync();  // all keys are written (and nobody reads a mailbox any more)
+  sort_candidates<SAMPLE_CTAS>(keys, n, (int)rank);  // ends at the cluster's barrier
   if (rank != 0) return;
   filtered_finish(row, best, inv_t, top_k, top_p, min_p, sum, keys, scratch_stride, n,
                   states + state_index[r], out + r);

@@ -473,6 +473,28 @@ def test_draws_over_a_wide_vocabulary(settings):
         assert got == want, step
 
 
+@pytest.mark.parametrize("settings", [dict(temperature=1.0, top_p=0.9),
+                                      dict(temperature=0.7, min_p=0.5),
+                                      dict(temperature=1.0, top_k=3000, top_p=0.99)])
+def test_filtered_draws_from_a_flat_distribution(settings):
+    """Nearly equal logits, as a model of random weights gives them: most of the vocabulary is
+    a candidate, so the sort runs over tens of thousands of keys (its steps in shared memory
+    and the far ones in global memory)."""
+    from mormot2_ai_b200.sampling import DeviceSampler, Sampling
+    V, rows, steps = 40003, 2, 6
+    g = torch.Generator().manual_seed(9)
+    sampler = DeviceSampler(torch.device(DEV), 2, V)
+    plain_samplers = [plain.PlainSampler(seed=3 + r, **settings) for r in range(rows)]
+    slots = torch.tensor([1, 0], dtype=torch.int32, device=DEV)
+    for r in range(rows):
+        sampler.start(int(slots[r]), 3 + r)
+    for step in range(steps):
+        logits = torch.randn(rows, V, generator=g) * 0.05
+        got = sampler.pick(logits.to(DEV), slots, Sampling(**settings)).tolist()
+        want = [plain_samplers[r].next(logits[r].numpy()) for r in range(rows)]
+        assert got == want, step
+
+
 def test_vocab_limit_is_never_crossed():
     from mormot2_ai_b200.sampling import DeviceSampler, Sampling
     sampler = DeviceSampler(torch.device(DEV), 2, 64)
