@@ -146,22 +146,39 @@ def timed_e2e(torch, eng, batch, steps, warmup, rng_seed):
     from mormot2_ai_b200.sampling import Sampling
 
     class TimedStepper(EngineStepper):
+        """Times the decode steps after the warm-up ones: an event before the launch of the
+        first of them, another after the host has read the last one's tokens (the requests'
+        caps end the run there, so nothing else is queued in between)."""
+
         def __init__(self, *a, **k):
             super().__init__(*a, **k)
-            self.calls = 0
+            self.launches = self.reads = 0
             self.e0 = torch.cuda.Event(enable_timing=True)
             self.e1 = torch.cuda.Event(enable_timing=True)
+            self.wall = [0.0, 0.0]
 
-        def pick(self, entries):
-            # call 0 is the prefill, calls 1..warmup warm up, the next `steps` are timed
-            if self.calls == warmup + 1:
-                self.h2d_bytes = self.d2h_bytes = 0
-                self.e0.record()
-            out = super().pick(entries)
-            if self.calls == warmup + steps:
-                self.e1.record()
-            self.calls += 1
-            return out
+        def decode(self, members):
+            run = super().decode(members)
+            launch, read = run.launch, run.read
+
+            def timed_launch():
+                if self.launches == warmup:
+                    self.h2d_bytes = self.d2h_bytes = 0
+                    self.e0.record()
+                    self.wall[0] = time.perf_counter()
+                launch()
+                self.launches += 1
+
+            def timed_read():
+                got = read()
+                self.reads += 1
+                if self.reads == warmup + steps:
+                    self.e1.record()
+                    self.wall[1] = time.perf_counter()
+                return got
+
+            run.launch, run.read = timed_launch, timed_read
+            return run
 
     prompt_len = CONTEXT - steps - warmup
     gen = torch.Generator().manual_seed(rng_seed)
@@ -171,7 +188,8 @@ def timed_e2e(torch, eng, batch, steps, warmup, rng_seed):
     generate(stepper, [Request(p, warmup + steps + 1, set(), i) for i, p in enumerate(prompts)])
     torch.cuda.synchronize()
     ms = stepper.e0.elapsed_time(stepper.e1)
-    return ms, stepper.h2d_bytes / steps, stepper.d2h_bytes / steps
+    wall_ms = (stepper.wall[1] - stepper.wall[0]) * 1e3
+    return ms, stepper.h2d_bytes / steps, stepper.d2h_bytes / steps, wall_ms
 
 
 def timed_prefill(torch, eng, tokens, repeats=3):
@@ -247,7 +265,7 @@ def main():
     clock_record = clocks.stop()
     value = BATCH * a.steps / (ms / 1e3)
     achieved = step_bytes(cfg, BATCH, mean_ctx) / (ms / a.steps / 1e3) / 1e9
-    e2e_ms, h2d, d2h = timed_e2e(torch, eng, BATCH, a.steps, a.warmup, 2)
+    e2e_ms, h2d, d2h, e2e_wall = timed_e2e(torch, eng, BATCH, a.steps, a.warmup, 2)
     out = {
         "metric": "Qwen3-8B decode tokens/s at batch 8, context 4096 (random BF16 weights)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps,

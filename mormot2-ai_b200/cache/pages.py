@@ -106,6 +106,9 @@ class CacheBook:
         self.slots = FreeList(max_slots, "slot")
         self.pools = [FreeList(p.n_pages, "page") for p in plans]
         self.length = [0] * max_slots
+        # the most positions that pages were ever reserved for since the slot was opened or
+        # cut to nothing: keys may have been written up to there, also by a step that failed
+        self.high = [0] * max_slots
         # pages[g][slot][i]: the page at entry i of the slot's table row, -1: none yet
         self.pages: List[List[List[int]]] = [
             [[] for _ in range(max_slots)] for _ in plans]
@@ -114,6 +117,7 @@ class CacheBook:
     def open(self) -> int:
         slot = self.slots.take()
         self.length[slot] = 0
+        self.high[slot] = 0
         return slot
 
     def close(self, slot: int) -> None:
@@ -168,10 +172,55 @@ class CacheBook:
                     page = self.pools[g].take()
                     self.pages[g][slot].append(page)
                     out[g].append((slot, len(self.pages[g][slot]) - 1, page))
+        for slot, new_length in requests:
+            self.high[slot] = max(self.high[slot], new_length)
         return out
 
     def commit(self, slot: int, new_length: int) -> None:
         self.length[slot] = new_length
+
+    # -- going back
+    def first_kept(self, g: int, slot: int) -> int:
+        """The first position whose keys group g still holds for the slot: 0, or where the
+        ring of pages of a windowed group began to overwrite itself."""
+        ring = self.plans[g].ring_pages
+        if not ring:
+            return 0
+        return max(0, pages_for(self.high[slot]) - ring) * PAGE
+
+    def truncate(self, slot: int, new_length: int) -> List[List[Tuple[int, int]]]:
+        """Shortens the slot's sequence to ``new_length`` positions. Whole pages beyond it go
+        back to their pools (the partly filled one stays); a group whose ring already wrapped
+        keeps its ring. Refused, with nothing changed, when a windowed group no longer holds
+        the keys that the position after ``new_length`` would read. Returns, per group, the
+        table entries ``(slot, entry)`` that were unmapped. The reference's
+        ``TDecoderContext.Truncate`` (``decoder.pas:996-1018``) shortens its one growing
+        buffer; pages and rings are this library's own."""
+        self.check_open(slot)
+        length = self.length[slot]
+        if not 0 <= new_length <= length:
+            raise CacheError(f"slot {slot}: truncate({new_length}) of {length} positions")
+        if new_length > 0:
+            for g, plan in enumerate(self.plans):
+                if plan.ring_pages and max(0, new_length - plan.window + 1) < self.first_kept(g, slot):
+                    raise CacheError(
+                        f"slot {slot}: truncate({new_length}): a sliding window of "
+                        f"{plan.window} no longer holds the keys of that position "
+                        f"(kept from {self.first_kept(g, slot)} on)")
+        out: List[List[Tuple[int, int]]] = [[] for _ in self.plans]
+        for g, plan in enumerate(self.plans):
+            held = self.pages[g][slot]
+            wrapped = (plan.ring_pages and pages_for(self.high[slot]) > plan.ring_pages
+                       and new_length > 0)
+            keep = len(held) if wrapped else min(len(held), self.entries_needed(g, new_length))
+            while len(held) > keep:
+                page = held.pop()
+                self.pools[g].give(page)
+                out[g].append((slot, len(held)))
+        self.length[slot] = new_length
+        if new_length == 0:
+            self.high[slot] = 0
+        return out
 
     # -- checks for tests
     def held_pages(self, g: int) -> int:

@@ -31,7 +31,7 @@ class CacheLine:
 
 class CacheStorage:
     def __init__(self, plans: List[GroupPlan], max_slots: int, dtype: torch.dtype,
-                 device: torch.device, state_shapes: Dict[int, Tuple[int, ...]]):
+                 device: torch.device, state_needs: Dict[int, "StateNeed"]):
         self.plans = plans
         self.pools: List[torch.Tensor] = []
         self.tables: List[torch.Tensor] = []
@@ -51,14 +51,20 @@ class CacheStorage:
                 self.lines[line] = CacheLine(pool[i, 0], pool[i, 1], table, plan.max_pages,
                                              plan.ring_pages, plan.window, plan.kv_heads,
                                              plan.head_dim)
-        # fixed-size state per slot, zero when a sequence starts
+        # fixed-size state per slot, at its initial value when a sequence starts; beside it a
+        # copy of the same size that a step saves the slots it touches into, so that a step
+        # that fails half way leaves the state it found
+        self.state_init: Dict[int, float] = {l: float(n.init) for l, n in state_needs.items()}
         self.states: Dict[int, torch.Tensor] = {
-            line: torch.zeros((max_slots,) + tuple(shape), dtype=torch.float32, device=device)
-            for line, shape in state_shapes.items()}
+            line: torch.full((max_slots,) + tuple(n.shape), float(n.init),
+                             dtype=getattr(torch, n.dtype), device=device)
+            for line, n in state_needs.items()}
+        self.saved: Dict[int, torch.Tensor] = {l: torch.empty_like(s)
+                                               for l, s in self.states.items()}
 
     def bytes(self) -> int:
         return (sum(p.numel() * p.element_size() for p in self.pools)
-                + sum(s.numel() * 4 for s in self.states.values()))
+                + sum(2 * s.numel() * s.element_size() for s in self.states.values()))
 
     def map_pages(self, new_entries: List[List[Tuple[int, int, int]]]) -> None:
         """Writes the new table entries of ``CacheBook.reserve`` to the device tables."""
@@ -73,5 +79,15 @@ class CacheStorage:
             self.tables[g][lo:hi + 1].copy_(host[lo:hi + 1])
 
     def reset_state(self, slot: int) -> None:
-        for s in self.states.values():
-            s[slot].zero_()
+        for line, s in self.states.items():
+            s[slot].fill_(self.state_init[line])
+
+    def save_states(self, slots: torch.Tensor) -> None:
+        """Keeps a copy of the state of ``slots`` (int64 indices on the device)."""
+        for line, s in self.states.items():
+            self.saved[line].index_copy_(0, slots, s.index_select(0, slots))
+
+    def restore_states(self, slots: torch.Tensor) -> None:
+        """Puts the copy of ``save_states`` back."""
+        for line, s in self.states.items():
+            s.index_copy_(0, slots, self.saved[line].index_select(0, slots))

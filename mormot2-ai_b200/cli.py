@@ -62,9 +62,9 @@ def llm_bench(argv: List[str]) -> int:
     logits = eng.step([Entry(s, p) for s, p in zip(slots, prompts)])
     ids = sampler.pick(logits, eng.last_slots, greedy).tolist()
     t1 = time.time()
-    for _ in range(a.new_tokens - 1):
-        logits = eng.step([Entry(s, [t]) for s, t in zip(slots, ids)])
-        ids = sampler.pick(logits, eng.last_slots, greedy).tolist()
+    if a.new_tokens > 1:
+        # the picks are fed back on the device; the host reads them when the last is chosen
+        eng.decode_steps(slots, ids, a.new_tokens - 1, sampler, greedy).cpu()
     t2 = time.time()
     eng.rt.check()
     print(f"prefill: {a.batch * a.prompt_tokens} tokens in {int((t1 - t0) * 1000)} ms = "

@@ -13,6 +13,8 @@ from typing import List, Sequence, Tuple
 import numpy as np
 import torch
 
+from ..errors import InferError
+
 
 @dataclass
 class StepContext:
@@ -54,7 +56,9 @@ class StepBuffers:
         B = len(seqs)
         T = sum(len(s[2]) for s in seqs)
         n_want = sum(len(s[3]) for s in seqs)
-        assert 0 < T <= self.max_tokens and B <= self.max_seqs and n_want <= self.max_tokens
+        if not (0 < T <= self.max_tokens and B <= self.max_seqs and n_want <= self.max_tokens):
+            raise InferError(f"a pass of {T} tokens, {B} sequences and {n_want} wanted rows; the "
+                             f"buffers take {self.max_tokens} tokens and {self.max_seqs} sequences")
         if self.in_flight:
             self.copied.synchronize()  # the last copy must have read the host buffer
         o_ids, o_seq, o_pos, o_tslot = 0, T, 2 * T, 3 * T

@@ -10,6 +10,7 @@ pages are this library's own.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
@@ -25,8 +26,11 @@ from ..errors import CacheError, InferError
 from ..weights.binding import bind_tensors
 from ..weights.safetensors_file import SafeTensorsFolder
 from .batch import StepBuffers, StepContext
+from .decode import DecodeRun
 from .model import DecoderModel
 from .runtime import Runtime
+
+MAX_GRAPHS = 24      # decode graphs kept (one per batch size and wanted rows), oldest use first out
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
           "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
@@ -76,14 +80,23 @@ class Engine:
                                  self.prefill_chunk)
         self.book = CacheBook(self.plans, self.max_slots, self.max_context)
         self.cache = CacheStorage(self.plans, self.max_slots, rt.dtype, rt.device,
-                                  {l: s.shape for l, s in self.model.state_needs.items()})
+                                  self.model.state_needs)
+        # whether a slot's fixed-size state holds exactly the slot's length (the reference's
+        # fStateOk, decoder.pas:436, :3301, :3348); only models with such state look at it
+        self.has_state = bool(self.model.state_needs)
+        self.state_ok = [True] * self.max_slots
+        # the token at every position of a slot, for prefix reuse (the reference's fIds,
+        # decoder.pas:412-421, Common :1264-1273)
+        self.ids: List[List[int]] = [[] for _ in range(self.max_slots)]
+        self.run: Optional[DecodeRun] = None             # the decode run that is open, if any
         self.buffers = StepBuffers(self.max_step_tokens, self.max_slots, rt.device)
         self.on_state: Optional[Callable[[str, torch.Tensor], None]] = None
         self.passes = 0  # passes of the model so far (a step of long prompts takes several)
         self.last_slots: Optional[torch.Tensor] = None   # slots of the last step, on the device
         # decode passes are replayed as CUDA graphs, one per (sequences, wanted rows)
         self.use_graphs = self.model.capturable()
-        self.graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
+        self.graphs: "OrderedDict[Tuple[int, int], _DecodeGraph]" = OrderedDict()
+        self.graph_pool = None                           # one memory pool for all of them
         self.last_h2d_bytes = 0                          # index bytes copied for the last step
 
     # ------------------------------------------------------------------ making one
@@ -111,14 +124,66 @@ class Engine:
 
     # ------------------------------------------------------------------ sequences
     def open(self) -> int:
-        """A slot for a new sequence (its fixed-size state zeroed)."""
+        """A slot for a new sequence (its fixed-size state at its initial value)."""
         slot = self.book.open()
         self.cache.reset_state(slot)
+        self.state_ok[slot] = True
+        self.ids[slot] = []
         return slot
 
     def close(self, slot: int) -> None:
         """Gives the slot and its pages back; later sequences use them again."""
+        if self.run is not None and slot in self.run.slots:
+            raise InferError(f"slot {slot} is part of the open decode run: finish it first")
         self.book.close(slot)
+        self.ids[slot] = []
+
+    def truncate(self, slot: int, length: int) -> None:
+        """Shortens the slot's sequence to its first ``length`` positions; the next step goes
+        on from there, and its logits are those of a fresh pass over the kept tokens and the
+        new ones. Whole pages beyond ``length`` go back to the pool. Refused when a sliding
+        window's ring no longer holds the keys before ``length``, and, for a model with
+        fixed-size state, for every length but 0 and the present one (such state cannot go
+        back). ``TDecoderContext.Truncate`` of the reference (``decoder.pas:996-1018``)."""
+        if self.run is not None and slot in self.run.slots:
+            raise InferError(f"slot {slot} is part of the open decode run: finish it first")
+        self.book.check_open(slot)
+        now = self.book.length[slot]
+        if self.has_state and length not in (0, now) and 0 <= length <= now:
+            raise CacheError(f"slot {slot}: truncate({length}): the fixed-size state of a "
+                             f"sequence of {now} tokens cannot go back there")
+        if self.has_state and length == now and not self.state_ok[slot]:
+            raise CacheError(f"slot {slot}: its fixed-size state does not hold its {now} "
+                             "tokens any more; only truncate(0) is left")
+        self.book.truncate(slot, length)
+        del self.ids[slot][length:]
+        if length == 0:
+            self.cache.reset_state(slot)
+            self.state_ok[slot] = True
+
+    def common(self, slot: int, tokens: Sequence[int]) -> int:
+        """How many of the slot's first tokens equal the first of ``tokens``
+        (``TDecoderContext.Common``, ``decoder.pas:1264-1273``)."""
+        self.book.check_open(slot)
+        held = self.ids[slot]
+        n = 0
+        while n < len(held) and n < len(tokens) and held[n] == int(tokens[n]):
+            n += 1
+        return n
+
+    def reuse(self, slot: int, tokens: Sequence[int]) -> int:
+        """Keeps of the slot what a new request of ``tokens`` can use again and returns that
+        many positions: the common prefix, but never the whole request, whose last token must
+        still be fed to give logits (``TDecoderModel.Reuse``, ``decoder.pas:3371-3388``).
+        When that prefix cannot be cut to (a window's ring, fixed-size state) nothing is
+        kept."""
+        n = min(self.common(slot, tokens), max(0, len(tokens) - 1))
+        try:
+            self.truncate(slot, n)
+        except CacheError:
+            n = 0
+            self.truncate(slot, 0)
+        return n
 
     def length(self, slot: int) -> int:
         self.book.check_open(slot)
@@ -128,9 +193,14 @@ class Engine:
     def step(self, entries: Sequence[Entry]) -> Optional[torch.Tensor]:
         """Appends each entry's tokens to its sequence and returns the logits
         ``[wanted, vocab]`` (float32, on the device) in the order of the entries and of their
-        ``want``; None when nothing is wanted. Nothing changes if an entry is refused."""
+        ``want``; None when nothing is wanted. Nothing changes if an entry is refused, and a
+        step that fails between its passes leaves lengths and fixed-size state as it found
+        them. The logits of a decode step lie in memory that the next decode step writes
+        again: copy them if they are to outlive it."""
         if not entries:
             raise InferError("a step without entries")
+        if self.run is not None:
+            raise InferError("a decode run is open: finish it before another step")
         seen = set()
         plan: List[Tuple[int, int, List[int], List[int]]] = []
         for e in entries:
@@ -158,31 +228,54 @@ class Engine:
             if past + len(tokens) > self.max_context:
                 raise CacheError(f"slot {e.slot}: {past} + {len(tokens)} positions exceed the "
                                  f"context of {self.max_context}")
+            if self.has_state and not self.state_ok[e.slot]:
+                raise CacheError(f"slot {e.slot}: its fixed-size state does not hold its "
+                                 f"{past} tokens (a step failed, or a decode run fed it "
+                                 "further than it kept): truncate it to 0 or close it")
             plan.append((e.slot, past, tokens, want))
+        if len(plan) > self.max_slots:
+            raise InferError(f"a step of {len(plan)} sequences; the engine has "
+                             f"{self.max_slots} slots")
+        n_want = sum(len(w) for _, _, _, w in plan)
+        passes = self._passes(plan)
+        for seqs, _ in passes:
+            if sum(len(s[3]) for s in seqs) > self.max_step_tokens:
+                raise InferError(f"a pass of the step wants more than {self.max_step_tokens} "
+                                 "rows of logits (max_step_tokens)")
         new_pages = self.book.reserve([(s, p + len(t)) for s, p, t, _ in plan])
         self.cache.map_pages(new_pages)
 
-        n_want = sum(len(w) for _, _, _, w in plan)
-        passes = self._passes(plan)
         out = None
         if n_want and len(passes) > 1:
             out = torch.empty((n_want, self.vocab_size), dtype=torch.float32, device=self.rt.device)
         self.last_h2d_bytes = 0
         self.last_passes = len(passes)
-        for seqs, dest in passes:
-            ctx = self.buffers.fill(seqs)
-            self.last_h2d_bytes += 4 * (4 * ctx.T + 3 * ctx.B + 1 + ctx.n_want)
-            self.last_slots = ctx.seq_slot
-            logits = self._forward(ctx)
-            self.passes += 1
-            if logits is not None:
-                if out is None and len(passes) == 1:
-                    out = logits
-                else:
-                    out.index_copy_(0, torch.tensor(dest, dtype=torch.long, device=out.device),
-                                    logits)
+        touched = None
+        if self.has_state:
+            touched = torch.tensor([p[0] for p in plan], dtype=torch.long, device=self.rt.device)
+            self.cache.save_states(touched)
+        try:
+            for seqs, dest in passes:
+                ctx = self.buffers.fill(seqs)
+                self.last_h2d_bytes += 4 * (4 * ctx.T + 3 * ctx.B + 1 + ctx.n_want)
+                self.last_slots = ctx.seq_slot
+                logits = self._forward(ctx)
+                self.passes += 1
+                if logits is not None:
+                    if out is None and len(passes) == 1:
+                        out = logits
+                    else:
+                        out.index_copy_(0, torch.tensor(dest, dtype=torch.long,
+                                                        device=out.device), logits)
+        except BaseException:
+            # lengths were not committed; keys written beyond them are never read; the state
+            # goes back to what the step found
+            if touched is not None:
+                self.cache.restore_states(touched)
+            raise
         for slot, past, tokens, _ in plan:
             self.book.commit(slot, past + len(tokens))
+            self.ids[slot].extend(int(t) for t in tokens)
         return out
 
     # ------------------------------------------------------------------ one pass
@@ -198,52 +291,88 @@ class Engine:
         g = self.graphs.get(key)
         if g is None:
             out = self.model.forward(ctx, self.cache)     # this step's result, computed eagerly
+            while len(self.graphs) >= MAX_GRAPHS:         # the graph used longest ago goes
+                self.graphs.popitem(last=False)
             self.graphs[key] = self._capture(ctx)         # the same launches, for later steps
             return out
+        self.graphs.move_to_end(key)
         g.graph.replay()
         K.Launches.count += g.launches
         return g.logits
 
     def _capture(self, ctx: StepContext) -> "_DecodeGraph":
+        """Captures a decode pass. All graphs allocate from one memory pool: one graph runs
+        at a time and each is complete in itself (its inputs are the index buffers, the page
+        tables and the cache, which lie outside the pool), so the activations of one may lie
+        where those of another lay."""
         graph = torch.cuda.CUDAGraph()
+        if self.graph_pool is None:
+            self.graph_pool = torch.cuda.graph_pool_handle()
         before = K.Launches.count
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, pool=self.graph_pool):
             logits = self.model.forward(ctx, self.cache)
         launches = K.Launches.count - before
         K.Launches.count = before                         # capturing launched nothing
         return _DecodeGraph(graph, logits, launches)
 
-    def decode_steps(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int, sampler,
-                     sampling, vocab_limit: Optional[int] = None) -> torch.Tensor:
-        """``n_steps`` decode steps of the sequences in ``slots`` without a host round trip:
-        ``tokens`` are fed first, then each step feeds what the sampler chose in the step before
-        (the token ids and positions move on in device memory). Returns the chosen tokens
-        ``[n_steps, sequences]`` (int32, on the device); the last row is not fed. No stop
-        token is looked at: the caller cuts the rows."""
-        if len(set(slots)) != len(slots) or len(tokens) != len(slots) or n_steps <= 0:
-            raise InferError("decode_steps: one token for each of distinct slots, n_steps > 0")
+    # ------------------------------------------------------------------ decoding on the device
+    def decode_run(self, slots: Sequence[int], tokens: Sequence[int], steps: Sequence[int],
+                   sampler, sampling, vocab_limit: Optional[int] = None,
+                   history: bool = False) -> DecodeRun:
+        """Opens a decode run (``engine/decode.py``): the sequences in ``slots`` are fed
+        ``tokens`` in its first step and from then on what the sampler chose for them in the
+        step before, in device memory. ``steps[i]``: the most steps sequence i takes part in;
+        its pages up to there are reserved now (all or nothing), and the run goes no further
+        than the smallest of them. Until the run is finished no other step may be made."""
+        if self.run is not None:
+            raise InferError("a decode run is open already")
+        if (len(set(slots)) != len(slots) or len(tokens) != len(slots)
+                or len(steps) != len(slots) or not slots):
+            raise InferError("a decode run: one token and one step count for each of "
+                             "distinct slots")
+        if len(slots) > self.max_slots:
+            raise InferError(f"a decode run of {len(slots)} sequences; the engine has "
+                             f"{self.max_slots} slots")
         seqs = []
-        for slot, t in zip(slots, tokens):
+        for slot, t, n in zip(slots, tokens, steps):
             self.book.check_open(slot)
             if not 0 <= int(t) < self.vocab_size:
-                raise InferError(f"slot {slot}: token {t} is outside the vocabulary")
+                raise InferError(f"slot {slot}: token {t} is outside the vocabulary of "
+                                 f"{self.vocab_size}")
             past = self.book.length[slot]
-            if past + n_steps > self.max_context:
-                raise CacheError(f"slot {slot}: {past} + {n_steps} positions exceed the "
+            if n <= 0 or past + n > self.max_context:
+                raise CacheError(f"slot {slot}: {past} + {n} positions exceed the "
                                  f"context of {self.max_context}")
+            if self.has_state and not self.state_ok[slot]:
+                raise CacheError(f"slot {slot}: its fixed-size state does not hold its "
+                                 f"{past} tokens: truncate it to 0 or close it")
             seqs.append((slot, past, [int(t)], [0]))
-        self.cache.map_pages(self.book.reserve([(s, p + n_steps) for s, p, _, _ in seqs]))
+        self.cache.map_pages(self.book.reserve(
+            [(s, p + n) for (s, p, _, _), n in zip(seqs, steps)]))
         ctx = self.buffers.fill(seqs)
+        self.last_h2d_bytes = 4 * (4 * ctx.T + 3 * ctx.B + 1 + ctx.n_want)
         self.last_slots, self.last_passes = ctx.seq_slot, 1
-        history = torch.empty((n_steps, ctx.B), dtype=torch.int32, device=self.rt.device)
-        for i in range(n_steps):
-            logits = self._forward(ctx)
-            chosen = sampler.pick(logits, ctx.seq_slot, sampling, vocab_limit)
-            K.advance_decode(ctx.tok_ids, ctx.tok_pos, chosen, history[i])
-            self.passes += 1
-        for slot, past, _, _ in seqs:
-            self.book.commit(slot, past + n_steps)
-        return history
+        self.run = DecodeRun(self, ctx, list(slots), [int(t) for t in tokens], min(steps),
+                             sampler, sampling, vocab_limit, history)
+        return self.run
+
+    def decode_steps(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int, sampler,
+                     sampling, vocab_limit: Optional[int] = None) -> torch.Tensor:
+        """``n_steps`` steps of a decode run without looking at what was chosen in between.
+        Returns the chosen tokens ``[n_steps, sequences]`` (int32, on the device); the last
+        row is not fed. No stop token is looked at: the caller cuts the rows."""
+        if n_steps <= 0:
+            raise InferError("decode_steps: n_steps > 0")
+        run = self.decode_run(slots, tokens, [n_steps] * len(slots), sampler, sampling,
+                              vocab_limit, history=True)
+        try:
+            for _ in range(n_steps):
+                run.launch()
+        except BaseException:
+            run.abandon()
+            raise
+        run.finish()
+        return run.history[:n_steps]
 
     def _passes(self, plan):
         """Cuts a step into passes of at most ``prefill_chunk`` new tokens per sequence and

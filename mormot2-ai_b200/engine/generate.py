@@ -8,8 +8,15 @@ cap <= 0 is refused (``:2147-2154``); the cap shrinks to ``limit - len(prompt) +
 (``:2155-2157``: token n is fed only when another one follows); the stop token is part of the
 result and is not fed back (``:2176-2178``). Batching is this library's own.
 
-The loop decides on the host and computes nothing: it drives a *stepper* (``open``, ``close``,
-``pick``), which in the product is the engine with the device sampler.
+The loop decides on the host and computes nothing: it drives a *stepper*, which in the
+product is the engine with the device sampler. ``stepper.prefill`` runs the prompts of a batch
+in one step and returns each sequence's first pick. ``stepper.decode`` opens a *run* over the
+sequences that go on: ``run.launch()`` queues a step in which every sequence is fed its last
+pick (on the device), ``run.read()`` returns the picks of the oldest unread step. The loop
+keeps one step queued behind the one it reads, so the device does not wait for the host; what
+it learns a step late (a stop token) ends the run: the steps already queued still count for
+the sequences that go on, which then form the next run. Caps are known beforehand, so a run
+is never launched beyond the step in which its first sequence reaches its cap.
 """
 from __future__ import annotations
 
@@ -50,52 +57,102 @@ def checked(requests: Sequence[Request], limit: int) -> List[Request]:
     return out
 
 
-def plan_batches(requests: Sequence[Request], max_batch: int, total_pages: int) -> List[List[int]]:
-    """Which requests run together: in order, as many as ``max_batch`` slots and the cache's
-    pages allow (a sequence may come to hold len(prompt) + max_new - 1 positions)."""
+def pages_needed(pools: Sequence[Tuple[int, int]], positions: int) -> List[int]:
+    """The pages of every pool that a sequence of ``positions`` positions holds.
+    ``pools[g] = (pages of the pool, ring)``: a windowed group keeps a ring of ``ring`` pages
+    per sequence however long it grows (0: every page is kept)."""
+    n = pages_for(positions)
+    return [min(n, ring) if ring else n for _, ring in pools]
+
+
+def plan_batches(requests: Sequence[Request], max_batch: int,
+                 pools: Sequence[Tuple[int, int]]) -> List[List[int]]:
+    """Which requests run together: in order, as many as ``max_batch`` slots and the pages of
+    every pool allow (a sequence may come to hold len(prompt) + max_new - 1 positions; in a
+    windowed group never more than its ring)."""
     batches: List[List[int]] = []
     cur: List[int] = []
-    pages = 0
+    used = [0] * len(pools)
     for i, r in enumerate(requests):
-        need = pages_for(len(r.prompt) + r.max_new - 1)
-        if need > total_pages:
-            raise InferError(f"request {i} needs {need} pages of the cache, which has {total_pages}")
-        if cur and (len(cur) >= max_batch or pages + need > total_pages):
+        need = pages_needed(pools, len(r.prompt) + r.max_new - 1)
+        for g, (have, _) in enumerate(pools):
+            if need[g] > have:
+                raise InferError(f"request {i} needs {need[g]} pages of the cache, "
+                                 f"which has {have}")
+        if cur and (len(cur) >= max_batch
+                    or any(u + n > have for u, n, (have, _) in zip(used, need, pools))):
             batches.append(cur)
-            cur, pages = [], 0
+            cur, used = [], [0] * len(pools)
         cur.append(i)
-        pages += need
+        used = [u + n for u, n in zip(used, need)]
     if cur:
         batches.append(cur)
     return batches
+
+
+AHEAD = 2      # steps launched before the oldest of them is read
 
 
 def generate(stepper, requests: Sequence[Request]) -> List[Outcome]:
     """Runs every request to its end and returns the new tokens of each, in request order."""
     reqs = checked(requests, stepper.context_limit())
     results: List[Optional[Outcome]] = [None] * len(reqs)
-    for batch in plan_batches(reqs, stepper.max_batch(), stepper.total_pages()):
+    for batch in plan_batches(reqs, stepper.max_batch(), stepper.pools()):
         live: Dict[int, int] = {}          # request index -> slot
         new: Dict[int, List[int]] = {i: [] for i in batch}
+
+        def take(i: int, token: int) -> bool:
+            """Books a pick of request i; True if it was its last."""
+            new[i].append(token)
+            stopped = token in reqs[i].stop
+            if stopped or len(new[i]) >= reqs[i].max_new:
+                results[i] = Outcome(new[i], stopped)
+                return True
+            return False
+
+        run = None
         try:
             for i in batch:
                 live[i] = stepper.open(reqs[i].seed)
-            feed = {i: reqs[i].prompt for i in batch}
+            picks = stepper.prefill([(live[i], reqs[i].prompt) for i in batch])
+            for i, token in zip(list(batch), picks):
+                if take(i, int(token)):
+                    stepper.close(live.pop(i))       # the slot is free for a later batch
             while live:
-                order = [i for i in batch if i in live]
-                picked = stepper.pick([(live[i], feed[i]) for i in order])
-                feed = {}
-                for i, token in zip(order, picked):
-                    token = int(token)
-                    new[i].append(token)
-                    stopped = token in reqs[i].stop
-                    if stopped or len(new[i]) >= reqs[i].max_new:
-                        results[i] = Outcome(new[i], stopped)
-                        stepper.close(live.pop(i))   # the slot is free for a later batch
-                    else:
-                        feed[i] = [token]
+                members = [i for i in batch if i in live]
+                left = [reqs[i].max_new - len(new[i]) for i in members]   # picks still allowed
+                run = stepper.decode([(live[i], new[i][-1], n) for i, n in zip(members, left)])
+                horizon = min(left)        # the step in which the first cap is reached
+                launched = n_read = 0
+                kept = [0] * len(members)
+                done = [False] * len(members)
+                while not any(done):
+                    while launched < horizon and launched - n_read < AHEAD:
+                        run.launch()
+                        launched += 1
+                    tokens = run.read()
+                    n_read += 1
+                    for m, i in enumerate(members):
+                        kept[m] += 1
+                        done[m] = take(i, int(tokens[m]))
+                while n_read < launched:
+                    # launched before the host knew that a sequence had ended: these steps
+                    # still count for the sequences that go on
+                    tokens = run.read()
+                    n_read += 1
+                    for m, i in enumerate(members):
+                        if not done[m]:
+                            kept[m] += 1
+                            done[m] = take(i, int(tokens[m]))
+                run.finish(kept)
+                run = None
+                for m, i in enumerate(members):
+                    if done[m]:
+                        stepper.close(live.pop(i))
         finally:
-            for slot in live.values():   # an error: nothing stays held
+            if run is not None:          # an error: nothing stays held
+                run.abandon()
+            for slot in live.values():
                 stepper.close(slot)
     return results  # type: ignore[return-value]
 
@@ -113,6 +170,7 @@ class EngineStepper:
         self._torch = torch
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self.decode_steps = 0
 
     def context_limit(self) -> int:
         return self.engine.max_context
@@ -120,8 +178,8 @@ class EngineStepper:
     def max_batch(self) -> int:
         return self._max_batch
 
-    def total_pages(self) -> int:
-        return min(p.n_pages for p in self.engine.plans) if self.engine.plans else 1 << 30
+    def pools(self) -> List[Tuple[int, int]]:
+        return [(p.n_pages, p.ring_pages) for p in self.engine.plans]
 
     def open(self, seed: int) -> int:
         slot = self.engine.open()
@@ -131,7 +189,8 @@ class EngineStepper:
     def close(self, slot: int) -> None:
         self.engine.close(slot)
 
-    def pick(self, entries: List[Tuple[int, List[int]]]) -> List[int]:
+    def prefill(self, entries: List[Tuple[int, List[int]]]) -> List[int]:
+        """The prompts in one step; each sequence's first pick, read on the host."""
         from .engine import Entry
         logits = self.engine.step([Entry(slot, tokens) for slot, tokens in entries])
         if self.engine.last_passes == 1:
@@ -146,8 +205,30 @@ class EngineStepper:
         self.h2d_bytes += self.engine.last_h2d_bytes
         if box is None:
             host = tokens.cpu()
-            rt.check_cheap()
+            rt.check()
             self.d2h_bytes += host.numel() * 4
             return host.tolist()
         self.d2h_bytes += (rows + 1) * 4
         return rt.read_tokens(rows)
+
+    def decode(self, members: List[Tuple[int, int, int]]):
+        """A decode run over ``members = [(slot, last pick, steps it may still take)]``."""
+        run = self.engine.decode_run([m[0] for m in members], [m[1] for m in members],
+                                     [m[2] for m in members], self.sampler, self.sampling,
+                                     self.vocab_limit)
+        self.h2d_bytes += self.engine.last_h2d_bytes
+        return _CountedRun(run, self)
+
+
+class _CountedRun:
+    """A decode run that books the bytes it brings to the host."""
+
+    def __init__(self, run, stepper):
+        self.run, self.stepper = run, stepper
+        self.launch, self.finish, self.abandon = run.launch, run.finish, run.abandon
+
+    def read(self) -> List[int]:
+        got = self.run.read()
+        self.stepper.d2h_bytes += 4 * (1 + len(got))
+        self.stepper.decode_steps += 1
+        return got

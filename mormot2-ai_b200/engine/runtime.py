@@ -10,6 +10,7 @@ from .. import kernels as K
 from ..errors import KernelError
 
 MAILBOX_TOKENS = 4096
+MAIL_RING = 4          # copies of the mailbox that may be on their way to the host at once
 
 
 class Runtime:
@@ -36,6 +37,9 @@ class Runtime:
         self.error_word = self.mailbox[:1]
         self.host_mailbox = torch.zeros(1 + MAILBOX_TOKENS, dtype=torch.int32).pin_memory()
         self.mail_event = torch.cuda.Event()
+        # the same for steps that are read a step late (engine/decode.py)
+        self.host_ring = torch.zeros((MAIL_RING, 1 + MAILBOX_TOKENS), dtype=torch.int32).pin_memory()
+        self.ring_events = [torch.cuda.Event() for _ in range(MAIL_RING)]
 
     def check(self) -> None:
         """Raises if a kernel recorded that one of its waits ran out (synchronizes)."""
@@ -61,9 +65,17 @@ class Runtime:
         self._raise_if(got[0])
         return got[1:]
 
-    def check_cheap(self) -> None:
-        """Like ``check`` for a caller that has just synchronized anyway."""
-        self.check()
+    def post_mail(self, k: int, rows: int) -> None:
+        """Queues a copy of the error word and the first ``rows`` tokens of the token box into
+        place ``k`` of the host ring; ``take_mail(k, rows)`` waits for it."""
+        self.host_ring[k, :1 + rows].copy_(self.mailbox[:1 + rows], non_blocking=True)
+        self.ring_events[k].record()
+
+    def take_mail(self, k: int, rows: int) -> list:
+        self.ring_events[k].synchronize()
+        got = self.host_ring[k, :1 + rows].tolist()
+        self._raise_if(got[0])
+        return got[1:]
 
     def libraries(self):
         """The kernel libraries that a model of this runtime needs."""

@@ -12,7 +12,9 @@ Interfaces (``rt`` is the ``Runtime``: device, activation dtype, kernels; ``step
 ``StepContext`` of ``engine/batch.py``: which token belongs to which sequence, at which
 position, in which slot):
 
-- Norm:      ``forward(x_f32[T, size], rows=None) -> h[R, size]`` in the activation dtype.
+- Norm:      ``forward(x_f32[T, size], rows=None) -> h[R, size]`` in the activation dtype. A
+             norm with ``accepts_pending = True`` also takes ``pending=`` (split sums of the
+             product before, which it adds into x first).
 - Position:  ``frequencies() -> (inv_freq_f32[rot_dim/2] on the device, rot_dim)``.
 - Mixer:     ``forward(h[T, hidden], x_f32[T, hidden], step, line, state, writes_cache)``:
              adds its output to the residual ``x`` in place and returns None. ``line`` is the
@@ -60,9 +62,11 @@ class CacheNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """State of fixed size that a mixer keeps for every sequence (float32), zero when a
-    sequence starts."""
+    """State of fixed size that a mixer keeps for every sequence: ``shape`` values of
+    ``dtype`` (a torch type by name) per slot, every one ``init`` when a sequence starts."""
     shape: Tuple[int, ...]
+    dtype: str = "float32"
+    init: float = 0.0
 
 
 class Part:

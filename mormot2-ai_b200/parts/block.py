@@ -32,11 +32,10 @@ class PreNormResidualBlock(Part):
         norm = self.norms[which]
         if pending is None:
             return norm.forward(x)
-        try:
+        if getattr(norm, "accepts_pending", False):
             return norm.forward(x, pending=pending)
-        except TypeError:              # a norm that knows nothing of pending sums
-            settle(x, pending)
-            return norm.forward(x)
+        settle(x, pending)             # a norm that knows nothing of pending sums
+        return norm.forward(x)
 
 
 def settle(x, pending) -> None:

@@ -12,6 +12,7 @@ from .base import NORMS, Part, TensorNeed
 
 class RmsNorm(Part):
     capturable = True
+    accepts_pending = True      # forward(..., pending=) adds split sums into x before it norms
 
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)

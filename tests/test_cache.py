@@ -83,6 +83,61 @@ def test_failed_reservation_changes_nothing():
     assert b.held_pages(0) == 4
 
 
+def test_truncate_gives_whole_pages_back():
+    b, plans = book()
+    win = [i for i, p in enumerate(plans) if p.window][0]
+    full = [i for i, p in enumerate(plans) if not p.window][0]
+    s0 = b.open()
+    b.reserve([(s0, 200)])
+    b.commit(s0, 200)
+    held = b.held_pages(full)
+    gone = b.truncate(s0, 70)                       # pages 2 and 3 of 4 go, page 1 stays partly
+    assert b.length[s0] == 70 and b.held_pages(full) == held - 2
+    assert sorted(gone[full]) == [(s0, 2), (s0, 3)] and len(b.pages[full][s0]) == 2
+    assert len(b.pages[win][s0]) == 2               # the ring had not wrapped: it shrinks too
+    b.reserve([(s0, 130)])                          # and grows again
+    b.commit(s0, 130)
+    assert len(b.pages[full][s0]) == 3
+    with pytest.raises(CacheError, match="truncate"):
+        b.truncate(s0, 131)
+    with pytest.raises(CacheError, match="truncate"):
+        b.truncate(s0, -1)
+    b.truncate(s0, 130)                             # to the present length: nothing changes
+    assert len(b.pages[full][s0]) == 3
+    b.truncate(s0, 0)
+    assert all(b.held_pages(g) == 0 for g in range(len(plans))) and b.length[s0] == 0
+    b.close(s0)
+    with pytest.raises(CacheError, match="not open"):
+        b.truncate(s0, 0)
+
+
+def test_truncate_behind_a_windows_ring_is_refused():
+    """The windowed group (window 100, ring of 4 pages) of a sequence of 400 positions holds
+    keys from position 192 on: a cut whose next position would read older keys is refused and
+    changes nothing; a cut that the ring still covers keeps the whole ring."""
+    b, plans = book()
+    win = [i for i, p in enumerate(plans) if p.window][0]
+    s0 = b.open()
+    b.reserve([(s0, 400)])
+    b.commit(s0, 400)
+    assert b.first_kept(win, s0) == (7 - 4) * PAGE == 192
+    held = [b.held_pages(g) for g in range(len(plans))]
+    with pytest.raises(CacheError, match="sliding window of 100 no longer holds"):
+        b.truncate(s0, 290)                         # the next position reads keys from 191 on
+    assert b.length[s0] == 400 and [b.held_pages(g) for g in range(len(plans))] == held
+    b.truncate(s0, 291)                             # reads from 192 on: still there
+    assert b.length[s0] == 291 and len(b.pages[win][s0]) == 4
+    assert len(b.pages[0][s0]) == pages_for(291)
+    # what the ring lost stays lost after the cut: positions before 192 cannot come back
+    with pytest.raises(CacheError, match="no longer holds"):
+        b.truncate(s0, 250)
+    b.reserve([(s0, 500)])
+    b.commit(s0, 500)
+    assert len(b.pages[win][s0]) == 4 and len(b.pages[0][s0]) == pages_for(500)
+    b.truncate(s0, 0)                               # to nothing is always allowed
+    assert all(b.held_pages(g) == 0 for g in range(len(plans)))
+
+
 def test_random_walk_loses_nothing():
     rng = random.Random(7)
     b, plans = book(max_tokens=2048, max_context=512, slots=6)
@@ -95,6 +150,14 @@ def test_random_walk_loses_nothing():
             s = rng.choice(list(live))
             b.close(s)
             del live[s]
+        elif r < 0.6 and live:
+            s = rng.choice(list(live))
+            n = rng.randint(0, live[s])
+            try:
+                b.truncate(s, n)
+                live[s] = n
+            except CacheError:
+                pass
         elif live:
             s = rng.choice(list(live))
             n = min(512, live[s] + rng.randint(1, 90))
@@ -108,7 +171,10 @@ def test_random_walk_loses_nothing():
             held = [p for s in range(6) for p in b.pages[g][s]]
             assert len(held) == len(set(held)) == b.held_pages(g)     # none held twice
             for s, n in live.items():
-                assert len(b.pages[g][s]) == b.entries_needed(g, n)
+                # a ring that wrapped before a cut may hold more than the length needs
+                assert len(b.pages[g][s]) >= b.entries_needed(g, n)
+                if not plan.ring_pages:
+                    assert len(b.pages[g][s]) == b.entries_needed(g, n)
         assert b.slots.free == 6 - len(live)
     for s in list(live):
         b.close(s)

@@ -167,6 +167,73 @@ def test_prompts_cut_into_passes(tiny, dtype):
     eng.rt.check()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_truncate_and_go_on_equals_a_fresh_pass(tiny, dtype):
+    """A sequence cut back to a prefix and fed other tokens gives the logits of a fresh pass
+    over the new sequence (the reference's ``TinyPromptReuse``, ``test.infer.qwen3.pas:870-986``);
+    whole pages beyond the cut come back to the pool."""
+    eng = engine_of(tiny, dtype, max_tokens=1024, max_slots=2)
+    first = tiny.tokens(120, seed=600)
+    slot = eng.open()
+    eng.step([Entry(slot, first)])
+    held = [eng.book.held_pages(g) for g in range(len(eng.plans))]
+    for cut, more in ((70, 9), (17, 50), (17, 3)):
+        eng.truncate(slot, cut)
+        assert eng.length(slot) == cut
+        other = tiny.tokens(more, seed=601 + more)
+        ids = first[:cut] + other
+        out = eng.step([Entry(slot, other, list(range(more)))]).cpu().numpy()
+        check(out, tiny.reference(ids)[cut:], dtype, f"after a cut to {cut}")
+        first = ids
+        out = eng.step([Entry(slot, [7])]).cpu().numpy()       # and a decode step after it
+        first = first + [7]
+        check(out, tiny.reference(first)[-1:], dtype, f"decoding after a cut to {cut}")
+    assert [eng.book.held_pages(g) for g in range(len(eng.plans))] == [1] * len(eng.plans)
+    assert held == [2] * len(eng.plans)
+    with pytest.raises(CacheError, match="truncate"):
+        eng.truncate(slot, eng.length(slot) + 1)
+    # the same prefix again for another request: only what differs is fed
+    request = first[:15] + tiny.tokens(6, seed=650)
+    kept = eng.reuse(slot, request)
+    assert kept == 15 == eng.length(slot) and eng.common(slot, request) == 15
+    out = eng.step([Entry(slot, request[kept:])]).cpu().numpy()
+    check(out, tiny.reference(request)[-1:], dtype, "after reuse")
+    assert eng.reuse(slot, request) == len(request) - 1          # the last token is fed again
+    out = eng.step([Entry(slot, request[-1:])]).cpu().numpy()
+    check(out, tiny.reference(request)[-1:], dtype, "the same request again")
+    eng.truncate(slot, 0)
+    assert all(eng.book.held_pages(g) == 0 for g in range(len(eng.plans)))
+    out = eng.step([Entry(slot, request[:3])]).cpu().numpy()
+    check(out, tiny.reference(request[:3])[-1:], dtype, "after a cut to nothing")
+    eng.rt.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_truncate_behind_a_windows_ring(tiny_b_model, dtype):
+    """Tiny B's middle layer has a window of 24; with passes of 16 tokens its keys live in a
+    ring of 2 pages. A cut whose next position would read keys that the ring has overwritten
+    is refused and changes nothing; one that the ring still covers works."""
+    tiny = tiny_b_model
+    eng = engine_of(tiny, dtype, prefill_chunk=16, max_slots=2)
+    ring = [g for g, p in enumerate(eng.plans) if p.ring_pages]
+    assert ring and eng.plans[ring[0]].ring_pages == 2
+    ids = tiny.tokens(200, seed=610)
+    slot = eng.open()
+    eng.step([Entry(slot, ids)])
+    with pytest.raises(CacheError, match="no longer holds"):
+        eng.truncate(slot, 100)                     # the ring holds keys from 128 on
+    assert eng.length(slot) == 200
+    out = eng.step([Entry(slot, [3])]).cpu().numpy()
+    check(out, tiny.reference(ids + [3])[-1:], dtype, "after the refusal")
+    eng.truncate(slot, 160)                         # reads keys from 137 on
+    other = tiny.tokens(30, seed=611)
+    out = eng.step([Entry(slot, other, [0, 13, 29])]).cpu().numpy()
+    check(out, tiny.reference(ids[:160] + other)[[160, 173, 189]], dtype, "after the cut")
+    assert eng.reuse(slot, ids[:90] + [1, 2]) == 0  # a prefix behind the ring: nothing is kept
+    assert eng.length(slot) == 0
+    eng.rt.check()
+
+
 def test_refused_steps_change_nothing(tiny_a_model):
     tiny = tiny_a_model
     eng = engine_of(tiny, "float32", max_tokens=128, max_slots=2)
@@ -186,6 +253,11 @@ def test_refused_steps_change_nothing(tiny_a_model):
         eng.step([Entry(7, [1])])
     with pytest.raises(CacheError):
         eng.step([Entry(s0, [1]), Entry(s1, tiny.tokens(128))])     # more pages than there are
+    small = engine_of(tiny, "float32", max_tokens=128, max_slots=2, max_step_tokens=16)
+    t0 = small.open()
+    with pytest.raises(InferError, match="rows of logits"):          # wanted rows may repeat
+        small.step([Entry(t0, ids, [0] * 17)])
+    assert small.length(t0) == 0 and small.book.held_pages(0) == 0
     assert eng.length(s0) == 10 and eng.length(s1) == 0 and eng.book.held_pages(0) == held
     ref = tiny.reference(ids + [5])
     out = eng.step([Entry(s0, [5])]).cpu().numpy()

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from mormot2_ai_b200 import (ConfigError, DecoderModel, Engine, Entry, LayerSpec, ModelSpec,
+from mormot2_ai_b200 import (CacheError, ConfigError, DecoderModel, Engine, Entry, LayerSpec, ModelSpec,
                              PartSpec, Qwen3Config, Run, Runtime)
 from mormot2_ai_b200.parts.block import settle
 from mormot2_ai_b200.parts import (FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Part, StateNeed,
@@ -284,6 +284,93 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
     out = eng.step([Entry(s2, b)]).cpu().numpy()
     ok, err = close(out, plain_toy_forward(cfg, spec, ref, b)[-1:], dtype)
     assert ok, err
+
+
+def test_a_failed_step_leaves_state_and_length_as_it_found_them():
+    """A long prompt runs as several passes, each of which moves the toy mixer's state on. The
+    third pass fails (made on the host: the mixer raises on a flagged call). The step then
+    counts for nothing: length and state are those from before it, and the same step again
+    gives the plain restatement's logits (the reference marks its state as not matching with
+    ``fStateOk``, ``decoder.pas:436``, ``:3301``, ``:3348``)."""
+
+    class Failing(RunningMeanMixer):
+        fail_at = None
+        calls = 0
+
+        def forward(self, h, x, step, line, state, writes_cache):
+            Failing.calls += 1
+            if Failing.calls == Failing.fail_at:
+                raise RuntimeError("made to fail")
+            super().forward(h, x, step, line, state, writes_cache)
+
+    register_mixer("running_mean", Failing)
+    cfg = tiny_b()
+    spec = toy_spec(cfg, [Run(0, 0), Run(1, 1), Run(2, 2)], ["attn", "toy", "attn"])
+    rt = Runtime(DT["float32"])
+    model = DecoderModel(spec)
+    weights = random_tensors(model.tensors(), 5, 0.05, 0.1, torch.bfloat16)
+    ref = {k: v.float().numpy() for k, v in weights.items()}
+    dev = {k: v.float().to(DEV) for k, v in weights.items()}
+    eng = Engine(cfg, dev, rt, max_tokens=1024, model=model, prefill_chunk=8, max_slots=2)
+    rng = np.random.default_rng(3)
+    ids = rng.integers(0, cfg.vocab_size, 50).tolist()
+    other = rng.integers(0, cfg.vocab_size, 9).tolist()
+    s0, s1 = eng.open(), eng.open()
+    eng.step([Entry(s0, ids[:10]), Entry(s1, other[:4])])
+    before = eng.cache.states[1].clone()
+    Failing.calls, Failing.fail_at = 0, 3
+    with pytest.raises(RuntimeError, match="made to fail"):
+        eng.step([Entry(s0, ids[10:]), Entry(s1, other[4:])])     # 5 passes of 8 tokens
+    Failing.fail_at = None
+    assert eng.length(s0) == 10 and eng.length(s1) == 4
+    assert torch.equal(eng.cache.states[1], before)
+    out = eng.step([Entry(s0, ids[10:]), Entry(s1, other[4:])]).cpu().numpy()
+    for row, seq in enumerate((ids, other)):
+        ok, err = close(out[row:row + 1], plain_toy_forward(cfg, spec, ref, seq)[-1:], "float32")
+        assert ok, (row, err)
+    # state of fixed size cannot go back: only to nothing, or to where it is
+    with pytest.raises(CacheError, match="cannot go back"):
+        eng.truncate(s0, 20)
+    eng.truncate(s0, 50)
+    eng.truncate(s0, 0)
+    assert float(eng.cache.states[1][s0].abs().max()) == 0.0
+    out = eng.step([Entry(s0, other)]).cpu().numpy()
+    ok, err = close(out, plain_toy_forward(cfg, spec, ref, other)[-1:], "float32")
+    assert ok, err
+    # a decode run that keeps fewer steps than it launched leaves state ahead of the length
+    from mormot2_ai_b200 import Sampling
+    from mormot2_ai_b200.sampling import DeviceSampler
+    sampler = DeviceSampler(rt.device, eng.max_slots, eng.vocab_size)
+    run = eng.decode_run([s0, s1], [1, 2], [4, 4], sampler, Sampling())
+    run.launch(), run.launch()
+    run.read(), run.read()
+    run.finish([2, 1])
+    assert eng.state_ok[s0] and not eng.state_ok[s1]
+    with pytest.raises(CacheError, match="fixed-size state"):
+        eng.step([Entry(s1, [3])])
+    eng.step([Entry(s0, [3])])
+    eng.truncate(s1, 0)
+    eng.step([Entry(s1, [3])])
+    register_mixer("running_mean", RunningMeanMixer)
+
+
+def test_state_of_another_type_and_start_value():
+    from mormot2_ai_b200.cache.storage import CacheStorage
+    store = CacheStorage([], 4, torch.bfloat16, torch.device(DEV),
+                         {3: StateNeed((2, 3), "int32", 7), 5: StateNeed((4,))})
+    assert store.states[3].dtype == torch.int32 and store.states[5].dtype == torch.float32
+    assert store.states[3].shape == (4, 2, 3) and int(store.states[3].min()) == 7
+    store.states[3][1] += 5
+    store.states[5][1] += 1.5
+    idx = torch.tensor([1, 2], device=DEV)
+    store.save_states(idx)
+    store.states[3][1:3] = 0
+    store.states[5][:] = 9.0
+    store.restore_states(idx)
+    assert store.states[3][1].tolist() == [[12] * 3] * 2 and store.states[3][2].tolist() == [[7] * 3] * 2
+    assert store.states[5][1].tolist() == [1.5] * 4 and store.states[5][0].tolist() == [9.0] * 4
+    store.reset_state(1)
+    assert int(store.states[3][1].max()) == 7 and float(store.states[5][1].max()) == 0.0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

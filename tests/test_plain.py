@@ -10,8 +10,10 @@ import pytest
 from tests.plain import qwen3_plain as plain
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-# the reference project's tests/data/infer-ref folder, when a checkout of it is at hand
-REFERENCE_FIXTURES = os.environ.get("MORMOT_REFERENCE_FIXTURES", "")
+# the reference project's tests/data/infer-ref folder: named by MORMOT_REFERENCE_FIXTURES, else
+# looked for in a checkout of the reference project beside this repository (../reference)
+REFERENCE_FIXTURES = os.environ.get("MORMOT_REFERENCE_FIXTURES") or os.path.join(
+    os.path.dirname(os.path.dirname(HERE)), "reference", "tests", "data", "infer-ref")
 
 
 def test_golden_record_against_the_reference_fixtures():
@@ -28,21 +30,26 @@ def test_golden_record_against_the_reference_fixtures():
 
 
 @pytest.mark.skipif(not os.path.isdir(REFERENCE_FIXTURES),
-                    reason="set MORMOT_REFERENCE_FIXTURES to the reference's tests/data/infer-ref")
+                    reason="no checkout of the reference project beside this repository; set "
+                           "MORMOT_REFERENCE_FIXTURES to its tests/data/infer-ref")
 def test_plain_matches_the_reference_fixtures_now():
     import hashlib
-    for name in ("tiny-qwen3", "tiny-qwen3-sliding"):
+    for name in ("tiny-qwen3", "tiny-qwen3/untied", "tiny-qwen3-sliding"):
         folder = os.path.join(REFERENCE_FIXTURES, name)
         config, weights = plain.read_model_folder(folder)
         manifest = json.load(open(os.path.join(folder, "manifest.json")))
         blob = open(os.path.join(folder, "tensors.bin"), "rb").read()
         assert hashlib.sha256(blob).hexdigest() == manifest["blob"]["sha256"]
         t = {e["name"]: e for e in manifest["tensors"]}
-        ids = np.frombuffer(blob[t["case1.ids"]["offset"]:][:t["case1.ids"]["bytes"]], np.int32)
-        e = t["case1.logits"]
-        want = np.frombuffer(blob[e["offset"]:][:e["bytes"]], np.float32).reshape(e["shape"])
-        got = plain.forward(config, weights, ids.tolist())
-        assert np.abs(got - want).max() < 5e-6
+        cases = sorted({k.split(".")[0] for k in t})
+        assert cases
+        for case in cases:
+            e = t[case + ".ids"]
+            ids = np.frombuffer(blob[e["offset"]:][:e["bytes"]], np.int32)
+            e = t[case + ".logits"]
+            want = np.frombuffer(blob[e["offset"]:][:e["bytes"]], np.float32).reshape(e["shape"])
+            got = plain.forward(config, weights, ids.tolist())
+            assert np.abs(got - want).max() < 5e-6, (name, case)
 
 
 def test_inverse_frequencies_round_as_the_reference():

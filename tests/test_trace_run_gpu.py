@@ -118,3 +118,26 @@ def test_steps_without_wants_write_nothing(tiny_a_model, tmp_path):
     got = logits_of(tmp_path, 1, tiny.config.vocab_size)
     ok, err = close(got, tiny.reference(ids)[-1:], "float32")
     assert ok, err
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_truncate_steps(tiny_b_model, dtype, tmp_path):
+    """A request is cut back to a prefix and goes on with other tokens, beside a request that
+    is left alone: the logits are those of the new sequence as a whole."""
+    tiny = tiny_b_model
+    a, b = tiny.tokens(80, seed=31), tiny.tokens(50, seed=32)
+    other = tiny.tokens(12, seed=33)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a, "want": [79]},
+                                {"id": "b", "tokens": b, "want": [49]}], "end": []},
+        {"step": 1, "truncate": [{"id": "a", "len": 17}],
+         "entries": [{"id": "a", "tokens": other[:1], "want": [0]},
+                     {"id": "b", "tokens": [9], "want": [0]}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": other[1:], "want": [0, 10]}], "end": ["a"]}]
+    replay(tiny.folder, dtype, steps, tmp_path, max_tokens=256)
+    vocab = tiny.config.vocab_size
+    new = a[:17] + other
+    ref_new, ref_b = tiny.reference(new), tiny.reference(b + [9])
+    for step, want in ((1, np.stack([ref_new[17], ref_b[50]])), (2, ref_new[[18, 28]])):
+        ok, err = close(logits_of(tmp_path, step, vocab), want, dtype)
+        assert ok, f"step {step}: relative error {err:.3g}"
