@@ -5,8 +5,17 @@
 A step is one decode step of a batch of 8 sequences whose context reaches 4,096 at the end of
 the timed steps. ``value`` is decoded tokens a second with the steps running back to back on
 the device (token ids and positions move on in device memory); ``e2e`` is the same through
-the Python entry point's loop: every step copies its token ids from pinned host memory to the
-device and reads the chosen tokens back. One JSON line is printed.
+the generation loop of the Python entry point, host token ids in and out: the prompts are
+copied in from pinned host memory, every step's picks are read back into pinned memory (with
+the kernels' error word) and looked at for stops and caps; a step's input ids are the step
+before's picks, which the engine keeps on the device, so in a steady batch no id travels back
+(``h2d_bytes_per_step`` counts what was copied: the index arrays whenever a run of steps is
+opened). Both go through ``Engine.decode_run``. One JSON line is printed.
+
+Beside the headline: ``prefill`` (2,048 tokens), ``points`` (tokens/s of decode at batch 1
+and 64, of prefills of 8,192 and 16,384 tokens, of the Qwen3-0.6B shape with 64 unequal
+prompts, and of the Qwen3-32B shape) with ``points_detail`` (each point's ms, bytes or flops,
+fraction of the measured peak and its own clock samples).
 """
 import argparse
 import json
@@ -22,6 +31,11 @@ sys.path.insert(0, ROOT)
 CONTEXT = 4096
 BATCH = 8
 PREFILL_TOKENS = 2048
+# Untimed decode steps between a batch's prefill and its warm-up steps, on the device-timed
+# and on the end-to-end path alike: the prefill of a whole batch holds the GPU at its power
+# cap, and for some tens of milliseconds afterwards a decode step runs up to a quarter slower
+# while the clocks come back (measured: 4.95 ms falling to 3.88 ms over 30 steps).
+SETTLE = 40
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -86,43 +100,65 @@ def model_config(layers):
                        rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
 
 
-def step_bytes(cfg, batch, context, itemsize=2):
+def shape_config(name):
+    """The other model shapes of the measurement (random weights, never loaded from disk)."""
+    from mormot2_ai_b200 import Qwen3Config
+    if name == "0.6B":
+        return Qwen3Config(vocab_size=151936, hidden_size=1024, num_hidden_layers=28,
+                           num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+                           intermediate_size=3072, max_position_embeddings=40960,
+                           rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True)
+    return Qwen3Config(vocab_size=151936, hidden_size=5120, num_hidden_layers=64,
+                       num_attention_heads=64, num_key_value_heads=8, head_dim=128,
+                       intermediate_size=25600, max_position_embeddings=40960,
+                       rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+
+
+def step_bytes(cfg, batch, tokens_held, itemsize=2):
     """What a decode step has to read: every weight it uses once (the embedding table only
     through its looked-up rows) and the keys and values of the live sequences."""
     h, i, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
     per_layer = ((cfg.q_width + 2 * cfg.kv_width) * h + h * cfg.q_width + 3 * h * i
                  + 2 * h + 2 * cfg.head_dim)
     weights = (cfg.num_hidden_layers * per_layer + h + v * h + batch * h) * itemsize
-    cache = batch * context * cfg.num_hidden_layers * 2 * cfg.kv_width * itemsize
+    # tokens_held: the summed lengths of the batch's sequences
+    cache = tokens_held * cfg.num_hidden_layers * 2 * cfg.kv_width * itemsize
     return weights + cache
 
 
-def prefill_flops(cfg, n):
+def prefill_flops(cfg, n, lens=None):
+    """Of one prompt of n tokens, or of prompts of ``lens`` tokens in one step."""
     h, i, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
-    per_layer = 2 * n * ((cfg.q_width + 2 * cfg.kv_width) * h + h * cfg.q_width + 3 * h * i)
-    attention = 4 * cfg.q_width * n * (n + 1) / 2
-    return cfg.num_hidden_layers * (per_layer + attention) + 2 * v * h
+    lens = [n] if lens is None else lens
+    total = sum(lens)
+    per_layer = 2 * total * ((cfg.q_width + 2 * cfg.kv_width) * h + h * cfg.q_width + 3 * h * i)
+    attention = sum(4 * cfg.q_width * m * (m + 1) / 2 for m in lens)
+    return cfg.num_hidden_layers * (per_layer + attention) + 2 * v * h * len(lens)
 
 
-def timed_decode(torch, eng, sampler, sampling, batch, steps, warmup, rng_seed):
-    """Prefills `batch` prompts so that warm-up and timed steps end at CONTEXT; returns the
-    device time of the timed steps (ms) and the mean context during them."""
+def timed_decode(torch, eng, sampler, sampling, lens, steps, warmup, rng_seed):
+    """Prefills prompts of ``lens`` tokens, decodes ``warmup`` steps, then times ``steps``
+    steps on the device. Returns the time (ms), the summed lengths of the sequences in the
+    middle of the timed steps, and the launches of the timed steps."""
     from mormot2_ai_b200 import Entry
     from mormot2_ai_b200 import kernels as K
-    prompt_len = CONTEXT - steps - warmup
     gen = torch.Generator().manual_seed(rng_seed)
-    slots = [eng.open() for _ in range(batch)]
+    slots = [eng.open() for _ in lens]
     for s in slots:
         sampler.start(s, s)
-    # prompts of different content; prefilled a few sequences at a time
-    firsts = []
-    for b0 in range(0, batch, 4):
-        part = slots[b0:b0 + 4]
-        prompts = [torch.randint(0, eng.vocab_size, (prompt_len,), generator=gen).tolist()
-                   for _ in part]
-        logits = eng.step([Entry(s, p) for s, p in zip(part, prompts)])
+    # prompts of different content, prefilled a few sequences at a time
+    firsts, b0 = [], 0
+    while b0 < len(lens):
+        b1, tokens = b0, 0
+        while b1 < len(lens) and (b1 == b0 or tokens + lens[b1] <= eng.max_step_tokens):
+            tokens += lens[b1]
+            b1 += 1
+        prompts = [torch.randint(0, eng.vocab_size, (n,), generator=gen).tolist()
+                   for n in lens[b0:b1]]
+        logits = eng.step([Entry(s, p) for s, p in zip(slots[b0:b1], prompts)])
         firsts += sampler.pick(logits, eng.last_slots, sampling).tolist()
-    hist = eng.decode_steps(slots, firsts, warmup, sampler, sampling)
+        b0 = b1
+    hist = eng.decode_steps(slots, firsts, SETTLE + warmup, sampler, sampling)
     nxt = hist[-1].tolist()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -136,7 +172,7 @@ def timed_decode(torch, eng, sampler, sampling, batch, steps, warmup, rng_seed):
     eng.rt.check()
     for s in slots:
         eng.close(s)
-    return ms, CONTEXT - steps / 2.0, launches
+    return ms, sum(lens) + len(lens) * (SETTLE + warmup + steps / 2.0), launches
 
 
 def timed_e2e(torch, eng, batch, steps, warmup, rng_seed):
@@ -155,62 +191,134 @@ def timed_e2e(torch, eng, batch, steps, warmup, rng_seed):
             self.launches = self.reads = 0
             self.e0 = torch.cuda.Event(enable_timing=True)
             self.e1 = torch.cuda.Event(enable_timing=True)
-            self.wall = [0.0, 0.0]
 
         def decode(self, members):
             run = super().decode(members)
             launch, read = run.launch, run.read
 
             def timed_launch():
-                if self.launches == warmup:
+                if self.launches == SETTLE + warmup:
                     self.h2d_bytes = self.d2h_bytes = 0
                     self.e0.record()
-                    self.wall[0] = time.perf_counter()
                 launch()
                 self.launches += 1
 
             def timed_read():
                 got = read()
                 self.reads += 1
-                if self.reads == warmup + steps:
+                if self.reads == SETTLE + warmup + steps:
                     self.e1.record()
-                    self.wall[1] = time.perf_counter()
                 return got
 
             run.launch, run.read = timed_launch, timed_read
             return run
 
-    prompt_len = CONTEXT - steps - warmup
+    prompt_len = CONTEXT - steps - warmup - SETTLE
     gen = torch.Generator().manual_seed(rng_seed)
     prompts = [torch.randint(0, eng.vocab_size, (prompt_len,), generator=gen).tolist()
                for _ in range(batch)]
     stepper = TimedStepper(eng, Sampling(), None, batch)
-    generate(stepper, [Request(p, warmup + steps + 1, set(), i) for i, p in enumerate(prompts)])
+    generate(stepper, [Request(p, SETTLE + warmup + steps + 1, set(), i)
+                       for i, p in enumerate(prompts)])
     torch.cuda.synchronize()
     ms = stepper.e0.elapsed_time(stepper.e1)
-    wall_ms = (stepper.wall[1] - stepper.wall[0]) * 1e3
-    return ms, stepper.h2d_bytes / steps, stepper.d2h_bytes / steps, wall_ms
+    return ms, stepper.h2d_bytes / steps, stepper.d2h_bytes / steps
 
 
-def timed_prefill(torch, eng, tokens, repeats=3):
+def timed_prefill(torch, eng, lens, repeats=3):
+    """One step over prompts of ``lens`` tokens (best of ``repeats`` after a warm-up run)."""
     from mormot2_ai_b200 import Entry
     gen = torch.Generator().manual_seed(7)
     best = None
     for r in range(repeats + 1):
-        ids = torch.randint(0, eng.vocab_size, (tokens,), generator=gen).tolist()
-        slot = eng.open()
+        prompts = [torch.randint(0, eng.vocab_size, (n,), generator=gen).tolist() for n in lens]
+        slots = [eng.open() for _ in lens]
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        eng.step([Entry(slot, ids)])
+        eng.step([Entry(s, p) for s, p in zip(slots, prompts)])
         e1.record()
         torch.cuda.synchronize()
-        eng.close(slot)
+        for s in slots:
+            eng.close(s)
         if r > 0:          # the first run warms up
             ms = e0.elapsed_time(e1)
             best = ms if best is None else min(best, ms)
     eng.rt.check()
     return best
+
+
+class Points:
+    """The extra measurements: tokens/s under ``points``, the rest under ``points_detail``."""
+
+    def __init__(self, pk):
+        self.pk, self.values, self.detail = pk, {}, {}
+
+    def decode(self, name, cfg, ms, steps, batch, tokens_held, clocks):
+        per_step = ms / steps
+        gbs = step_bytes(cfg, batch, tokens_held) / (per_step / 1e3) / 1e9
+        self.values[name] = round(batch * steps / (ms / 1e3), 1)
+        self.detail[name] = {"ms_per_step": round(per_step, 4), "steps": steps, "batch": batch,
+                             "gb_per_step": round(step_bytes(cfg, batch, tokens_held) / 1e9, 3),
+                             "gbs": round(gbs, 1), "frac_hbm": round(gbs / self.pk["hbm_gbs"], 4),
+                             "clocks": clocks}
+
+    def prefill(self, name, cfg, ms, lens, clocks, passes=1):
+        flops = prefill_flops(cfg, 0, lens)
+        self.values[name] = round(sum(lens) / (ms / 1e3), 1)
+        self.detail[name] = {"ms": round(ms, 3), "tokens": sum(lens), "prompts": len(lens),
+                             "tflop": round(flops / 1e12, 2), "passes": passes,
+                             "frac_bf16": round(flops / (ms / 1e3) / (self.pk["bf16_tflops"] * 1e12), 4),
+                             "clocks": clocks}
+
+
+def clocked(fn, *args, **kw):
+    clocks = Clocks()
+    clocks.start()
+    try:
+        out = fn(*args, **kw)
+    finally:
+        record = clocks.stop()
+    return out, record
+
+
+def other_shapes(torch, a, pts):
+    """The Qwen3-0.6B shape with 64 prompts of unequal lengths (one prefill step, then 256
+    decode steps) and the Qwen3-32B shape (prefill of 2,048 tokens, decode at batch 1 and 8
+    toward a context of 4,096). Each engine is made, measured and dropped."""
+    from mormot2_ai_b200 import Engine
+    from mormot2_ai_b200.sampling import DeviceSampler, Sampling
+    greedy = Sampling()
+    # -- 0.6B, ragged
+    cfg = shape_config("0.6B")
+    lens = torch.randint(16, 2049, (64,), generator=torch.Generator().manual_seed(3)).tolist()
+    steps, warm = 256, max(a.warmup, 3)
+    room = sum(-(-(n + steps + warm + SETTLE + 1) // 64) * 64 for n in lens)
+    eng = Engine.from_random(cfg, seed=3, std=0.02, max_tokens=room, max_context=2048 + 512,
+                             max_slots=64, prefill_chunk=2048, max_step_tokens=sum(lens))
+    sampler = DeviceSampler(eng.rt.device, eng.max_slots, eng.vocab_size)
+    ms, rec = clocked(timed_prefill, torch, eng, lens)
+    pts.prefill("ragged_0p6b_prefill", cfg, ms, lens, rec)
+    (ms, held, _), rec = clocked(timed_decode, torch, eng, sampler, greedy, lens, steps, warm, 30)
+    pts.decode("ragged_0p6b_decode", cfg, ms, steps, 64, held, rec)
+    pts.detail["ragged_0p6b_decode"]["prompt_lens"] = f"uniform 16..2048, seed 3, sum {sum(lens)}"
+    del eng, sampler
+    torch.cuda.empty_cache()
+    # -- 32B
+    cfg = shape_config("32B")
+    eng = Engine.from_random(cfg, seed=4, std=0.02, max_tokens=8 * CONTEXT, max_context=CONTEXT,
+                             max_slots=8, prefill_chunk=2048, max_step_tokens=8192)
+    sampler = DeviceSampler(eng.rt.device, eng.max_slots, eng.vocab_size)
+    ms, rec = clocked(timed_prefill, torch, eng, [PREFILL_TOKENS], repeats=2)
+    pts.prefill("qwen3_32b_prefill", cfg, ms, [PREFILL_TOKENS], rec)
+    steps = min(a.steps, 64)
+    for b in (1, 8):
+        lens = [CONTEXT - steps - warm - SETTLE] * b
+        (ms, held, _), rec = clocked(timed_decode, torch, eng, sampler, greedy, lens, steps, warm,
+                                     40 + b)
+        pts.decode(f"qwen3_32b_decode_b{b}", cfg, ms, steps, b, held, rec)
+    del eng, sampler
+    torch.cuda.empty_cache()
 
 
 def main():
@@ -221,10 +329,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=36, help="fewer layers than the 36 of the shape "
                     "(named in config); the layer sizes stay")
-    ap.add_argument("--skip-points", action="store_true", help="no batch 1 / 64 / prefill runs")
+    ap.add_argument("--skip-points", action="store_true", help="only the headline: no prefill, "
+                    "no other batch sizes, no other shapes")
+    ap.add_argument("--skip-shapes", action="store_true", help="not the 0.6B and 32B shapes")
     ap.add_argument("--batches", default="1,64", help="batch sizes of the extra decode points")
-    ap.add_argument("--only-prefill", action="store_true",
-                    help="only the 2,048-token prefill (for profiles; prints its own short line)")
+    ap.add_argument("--long-prefills", default="8192,16384",
+                    help="token counts of the long prefill points (one sequence each)")
+    ap.add_argument("--only-prefill", type=int, nargs="?", const=PREFILL_TOKENS, default=0,
+                    help="only a prefill of this many tokens (for profiles; prints a short line)")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -236,7 +348,7 @@ def main():
               "(this library has no multi-GPU path)")
         return 2
     a.warmup = max(a.warmup, 3)
-    if a.steps < 1 or a.steps + a.warmup > CONTEXT - 64:
+    if a.steps < 1 or a.steps + a.warmup + SETTLE > CONTEXT - 64:
         print(f"bench.py: --steps + --warmup must leave a prompt of at least 64 tokens in the "
               f"context of {CONTEXT}")
         return 2
@@ -246,26 +358,34 @@ def main():
 
     pk = peaks()
     cfg = model_config(a.layers)
+    longs = [] if (a.skip_points or a.only_prefill) else [int(v) for v in a.long_prefills.split(",") if v]
     max_batch = BATCH if (a.skip_points or a.only_prefill) else 64
-    eng = Engine.from_random(cfg, seed=2, std=0.02, max_tokens=max_batch * CONTEXT,
-                             max_context=CONTEXT, max_slots=max_batch, prefill_chunk=2048,
+    context = max([CONTEXT, a.only_prefill] + longs)
+    eng = Engine.from_random(cfg, seed=2, std=0.02, max_tokens=max(max_batch * CONTEXT, context),
+                             max_context=context, max_slots=max_batch, prefill_chunk=4096,
                              max_step_tokens=8192)
     sampler = DeviceSampler(eng.rt.device, eng.max_slots, eng.vocab_size)
     greedy = Sampling()
     if a.only_prefill:
-        pms = timed_prefill(torch, eng, PREFILL_TOKENS, repeats=1)
-        print(json.dumps({"prefill_ms": round(pms, 3), "layers": a.layers}))
+        pms = timed_prefill(torch, eng, [a.only_prefill], repeats=1)
+        print(json.dumps({"prefill_ms": round(pms, 3), "tokens": a.only_prefill,
+                          "layers": a.layers}))
         return 0
-    # the prefill first, as the burst that it is in service (and as the burst peak is measured);
-    # the decode runs after it hold the GPU at its power cap for seconds
-    pms = None if a.skip_points else timed_prefill(torch, eng, PREFILL_TOKENS)
-    clocks = Clocks()
-    clocks.start()
-    ms, mean_ctx, launches = timed_decode(torch, eng, sampler, greedy, BATCH, a.steps, a.warmup, 1)
-    clock_record = clocks.stop()
+    pts = Points(pk)
+    # the prefills first, as the bursts that they are in service (and as the burst peak is
+    # measured); the decode runs after them hold the GPU at its power cap for seconds
+    pms = prefill_clocks = None
+    if not a.skip_points:
+        pms, prefill_clocks = clocked(timed_prefill, torch, eng, [PREFILL_TOKENS])
+        for n in longs:
+            ms, rec = clocked(timed_prefill, torch, eng, [n], repeats=2)
+            pts.prefill(f"prefill_{n}", cfg, ms, [n], rec, passes=-(-n // eng.prefill_chunk))
+    lens = [CONTEXT - a.steps - a.warmup - SETTLE] * BATCH
+    (ms, held, launches), clock_record = clocked(timed_decode, torch, eng, sampler, greedy, lens,
+                                                 a.steps, a.warmup, 1)
     value = BATCH * a.steps / (ms / 1e3)
-    achieved = step_bytes(cfg, BATCH, mean_ctx) / (ms / a.steps / 1e3) / 1e9
-    e2e_ms, h2d, d2h, e2e_wall = timed_e2e(torch, eng, BATCH, a.steps, a.warmup, 2)
+    achieved = step_bytes(cfg, BATCH, held) / (ms / a.steps / 1e3) / 1e9
+    e2e_ms, h2d, d2h = timed_e2e(torch, eng, BATCH, a.steps, a.warmup, 2)
     out = {
         "metric": "Qwen3-8B decode tokens/s at batch 8, context 4096 (random BF16 weights)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps,
@@ -279,13 +399,15 @@ def main():
             "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
             "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
             "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_norm_eps, "tied_head": False,
-            "prompt_tokens": CONTEXT - a.steps - a.warmup, "prefill_tokens": PREFILL_TOKENS,
+            "prompt_tokens": CONTEXT - a.steps - a.warmup - SETTLE, "settle_steps": SETTLE,
+            "prefill_tokens": PREFILL_TOKENS,
             "l2": "a step reads its weights (>15 GB), far larger than L2",
             "peaks": pk["source"],
-            "prefill_timing": "best of 3 after 1 warm-up, before the decode runs",
         },
         "e2e": {"value": round(BATCH * a.steps / (e2e_ms / 1e3), 1), "unit": "tokens/s",
-                "h2d_bytes_per_step": round(h2d, 1), "d2h_bytes_per_step": round(d2h, 1)},
+                "h2d_bytes_per_step": round(h2d, 1), "d2h_bytes_per_step": round(d2h, 1),
+                "inputs": "a step's ids are the step before's picks and stay on the device; "
+                          "prompts and index arrays come from pinned host memory"},
         "gpu_launches": launches,
         "clocks": clock_record,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
@@ -295,13 +417,23 @@ def main():
         flops = prefill_flops(cfg, PREFILL_TOKENS)
         out["prefill"] = {"value": round(PREFILL_TOKENS / (pms / 1e3), 1), "tokens": PREFILL_TOKENS,
                           "ms": round(pms, 3),
-                          "frac": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
-        points = {}
+                          "frac": round(flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                          "timing": "best of 3 after 1 warm-up, before the decode runs",
+                          "clocks": prefill_clocks}
         for b in [int(v) for v in a.batches.split(',') if v]:
             steps = min(a.steps, 128)
-            bms, _, _ = timed_decode(torch, eng, sampler, greedy, b, steps, a.warmup, 10 + b)
-            points[f"decode_b{b}"] = round(b * steps / (bms / 1e3), 1)
-        out["points"] = points
+            lens = [CONTEXT - steps - a.warmup - SETTLE] * b
+            (bms, held, _), rec = clocked(timed_decode, torch, eng, sampler, greedy, lens, steps,
+                                          a.warmup, 10 + b)
+            pts.decode(f"decode_b{b}", cfg, bms, steps, b, held, rec)
+        e1_ms, _, _ = timed_e2e(torch, eng, 1, min(a.steps, 128), a.warmup, 3)
+        pts.values["e2e_b1"] = round(min(a.steps, 128) / (e1_ms / 1e3), 1)
+        del eng, sampler
+        torch.cuda.empty_cache()
+        if not a.skip_shapes and a.layers == 36:
+            other_shapes(torch, a, pts)
+        out["points"] = pts.values
+        out["points_detail"] = pts.detail
     print(json.dumps(out))
     return 0
 

@@ -37,6 +37,9 @@ def llm_bench(argv: List[str]) -> int:
     ap.add_argument("new_tokens", nargs="?", type=int, default=32)
     ap.add_argument("weights", nargs="?", default="bf16", help="bf16 (default) | f32")
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together")
+    ap.add_argument("--shares", action="store_true",
+                    help="also time the kernels of one prefill and of the decode steps by class "
+                         "(products, attention, norms, rotary, ...), run one by one")
     a = ap.parse_args(argv)
     if a.prompt_tokens < 1 or a.new_tokens < 1:
         print("prompt tokens and new tokens: at least 1 each")
@@ -72,7 +75,30 @@ def llm_bench(argv: List[str]) -> int:
     if a.new_tokens > 1:
         print(f"decode: {a.batch * (a.new_tokens - 1)} tokens in {int((t2 - t1) * 1000)} ms = "
               f"{a.batch * (a.new_tokens - 1) / (t2 - t1):.1f} tokens/s")
+    if a.shares:
+        for s in slots:
+            eng.truncate(s, 0)
+        logits, shares, total = eng.timed_step([Entry(s, p) for s, p in zip(slots, prompts)])
+        _print_shares("prefill", shares, total)
+        ids = sampler.pick(logits, eng.last_slots, greedy).tolist()
+        sums, whole = {}, 0.0
+        n = min(a.new_tokens, 16)
+        for _ in range(n):
+            logits, shares, total = eng.timed_step([Entry(s, [t]) for s, t in zip(slots, ids)])
+            ids = sampler.pick(logits, eng.last_slots, greedy).tolist()
+            whole += total
+            for k, v in shares.items():
+                sums[k] = sums.get(k, 0.0) + v
+        _print_shares(f"decode, mean of {n} steps", {k: v / n for k, v in sums.items()}, whole / n)
     return 0
+
+
+def _print_shares(what: str, shares: dict, total: float) -> None:
+    """Where the time of a step goes, by class of kernel, largest first."""
+    in_kernels = sum(shares.values())
+    print(f"{what}: {total * 1000:.0f} us, {in_kernels * 1000:.0f} us in kernels run one by one")
+    for name, ms in sorted(shares.items(), key=lambda kv: -kv[1]):
+        print(f"  {name:<10} {ms * 1000:9.1f} us {100 * ms / max(in_kernels, 1e-9):5.1f} %")
 
 
 def llm_quickstart(argv: List[str]) -> int:

@@ -28,7 +28,8 @@ NVCC_FLAGS = [
     "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
 
-# more flags for experiments, e.g. MORMOT_B200_NVCC_FLAGS="-DMB_PDL_EARLY"
+# more flags for nvcc, e.g. MORMOT_B200_NVCC_FLAGS="-DMB_WAIT_LIMIT=1024" (the iteration limit of
+# the kernels' bounded waits); they are part of the built library's name
 NVCC_FLAGS += os.environ.get("MORMOT_B200_NVCC_FLAGS", "").split()
 
 # library name -> source file; headers that every library depends on

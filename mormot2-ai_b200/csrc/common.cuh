@@ -43,15 +43,6 @@ __device__ __forceinline__ void mb_grid_launch_next() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-static bool mb_pdl_enabled() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("MORMOT_B200_PDL");
-    on = (e && e[0] == '0') ? 0 : 1;
-  }
-  return on != 0;
-}
-
 template <typename... KArgs, typename... Args>
 static cudaError_t mb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                              cudaStream_t stream, Args... args) {
@@ -64,7 +55,7 @@ static cudaError_t mb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = mb_pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
@@ -85,7 +76,7 @@ static cudaError_t mb_launch_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = mb_pdl_enabled() ? 2 : 1;
+  cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

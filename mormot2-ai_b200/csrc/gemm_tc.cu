@@ -475,8 +475,6 @@ static int pair_capacity(int sms) {
   static int pairs = -1;
   if (pairs >= 0) return pairs;
   pairs = 0;
-  const char* e = getenv("MORMOT_B200_PAIR");
-  if (e && e[0] == '0') return pairs;
   if (cudaFuncSetAttribute(gemm_tc_pair_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            Tc2Cfg<256>::SMEM) != cudaSuccess) {
     cudaGetLastError();
@@ -519,7 +517,7 @@ static cudaError_t mb_launch_pair(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = mb_pdl_enabled() ? 2 : 1;
+  cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
@@ -551,13 +549,6 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, 
 // whose rounds of tiles take the least time (measured: a full round of tiles of width w takes
 // about w + 40 in units of 0.09 microseconds at K = 4096).
 static int pair_tile_width(int N, int tiles_m, int pairs) {
-  static int forced = -1;  // MORMOT_B200_PAIR_WIDTH: one width for every product (measurements)
-  if (forced < 0) {
-    const char* e = getenv("MORMOT_B200_PAIR_WIDTH");
-    forced = e ? atoi(e) : 0;
-    if (forced < 128 || forced > 256 || forced % 16) forced = 0;
-  }
-  if (forced) return forced;
   int best = 256;
   long long best_cost = -1;
   for (int w = 256; w >= 128; w -= 16) {
@@ -782,4 +773,29 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     MB_CHECK_LAUNCH("mb_gemm_tc reduce");
   }
   return 0;
+}
+
+// ------------------------------------------------------------------ the bounded wait, by itself
+// One warp waits on a barrier that nothing ever completes, with a limit of `tries` (a few
+// thousand: milliseconds), gives up, records `code` in *error and returns: the way every wait
+// of the kernels above ends when what it waits for never comes. It holds no tensor memory and
+// has no copy in flight, so there is nothing else to release.
+__global__ void wait_selftest_kernel(int* error, int code, unsigned tries, int* gave_up) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait_tries(b, 0, error, code, tries);
+    *gave_up = ok ? 0 : 1;
+  }
+}
+
+MB_EXPORT int mb_wait_selftest(int* error, int code, unsigned tries, int* gave_up, void* stream) {
+  if (tries == 0 || tries > (1u << 16)) MB_FAIL("mb_wait_selftest: 1 to 65536 tries, not %u", tries);
+  wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(error, code, tries, gave_up);
+  MB_CHECK_LAUNCH("mb_wait_selftest");
 }

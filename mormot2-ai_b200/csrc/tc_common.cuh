@@ -50,14 +50,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // The limit of every wait: each try_wait already suspends for a while in hardware, so this is
 // seconds, far beyond any healthy wait, and still an end.
+#ifndef MB_WAIT_LIMIT
 #define MB_WAIT_LIMIT (1u << 22)
+#endif
 
-// false after MB_WAIT_LIMIT tries; then *error (global) holds `code` and the caller goes on.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error, int code) {
-  for (uint32_t i = 0; i < MB_WAIT_LIMIT; ++i)
+// false after `limit` tries; then *error (global) holds `code` and the caller goes on.
+__device__ __forceinline__ bool mbar_wait_tries(uint32_t bar, uint32_t parity, int* error, int code,
+                                                uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   if (error) atomicCAS(error, 0, code);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error, int code) {
+  return mbar_wait_tries(bar, parity, error, code, MB_WAIT_LIMIT);
 }
 
 // ---------------------------------------------------------------------------- TMA

@@ -110,6 +110,7 @@ class Engine:
         rt = Runtime(DTYPES[dtype], device, kwargs.pop("fast_kernels", True))
         model = DecoderModel(config.to_model_spec())
         weights = bind_tensors(model.tensors(), SafeTensorsFolder(folder), rt.dtype, rt.device)
+        rt.consume_weights = True
         return cls(config, weights, rt, model=model, **kwargs)
 
     @classmethod
@@ -120,6 +121,7 @@ class Engine:
         rt = Runtime(DTYPES[dtype], device, kwargs.pop("fast_kernels", True))
         model = DecoderModel(config.to_model_spec())
         weights = random_tensors(model.tensors(), seed, std, norm_std, rt.dtype, device)
+        rt.consume_weights = True
         return cls(config, weights, rt, model=model, **kwargs)
 
     # ------------------------------------------------------------------ sequences
@@ -277,6 +279,24 @@ class Engine:
             self.book.commit(slot, past + len(tokens))
             self.ids[slot].extend(int(t) for t in tokens)
         return out
+
+    def timed_step(self, entries: Sequence[Entry]):
+        """``step`` with its kernels run one by one and timed by class: returns the logits, the
+        milliseconds of each class (products, attention, norms, rotary, embedding, ...) and
+        of the whole step. Graphs are off for it and every kernel waits for the one before, so
+        the sum is larger than the step of the product path; the shares say where time goes
+        (the reference's ``llm-bench`` prints the same, ``demos/infer/llm-bench.lpr:499-527``)."""
+        graphs, self.use_graphs = self.use_graphs, False
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        try:
+            with K.Timing() as timing:
+                e0.record()
+                logits = self.step(entries)
+                e1.record()
+        finally:
+            self.use_graphs = graphs
+        shares = timing.shares(e0, e1)
+        return logits, shares, e0.elapsed_time(e1)
 
     # ------------------------------------------------------------------ one pass
     def _forward(self, ctx: StepContext) -> Optional[torch.Tensor]:

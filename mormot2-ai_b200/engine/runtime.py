@@ -23,6 +23,9 @@ class Runtime:
         # the tensor-core kernels serve the bfloat16 path only; the 32-bit path multiplies and
         # adds in float32 throughout
         self.fast_kernels = fast_kernels and dtype == torch.bfloat16
+        # True: the tensors handed to ``bind`` belong to the engine alone, and a part that
+        # re-lays a weight out (fused q/k/v, interleaved gate and up) drops the original
+        self.consume_weights = False
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         # scratch of the split matrix products (float32) and the word that kernels set when
         # one of their bounded waits ran out

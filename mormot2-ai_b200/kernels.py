@@ -61,15 +61,73 @@ class Launches:
     count = 0
 
 
+CLASS_OF = {"mb_gemm_tc": "products", "mb_gemm_simt": "products",
+            "mb_attention_simt": "attention", "mb_attention_decode": "attention",
+            "mb_attention_decode_clusters": "attention", "mb_attention_prefill": "attention",
+            "mb_attention_prefill_tc": "attention", "mb_rmsnorm": "norms",
+            "mb_qk_norm_rope_store": "rotary", "mb_embed": "embedding", "mb_swiglu": "activation",
+            "mb_argmax": "sampling", "mb_sample": "sampling", "mb_sample_filtered": "sampling",
+            "mb_advance_decode": "sampling"}
+
+
+class Timing:
+    """Times every kernel call by its class while it is open (CUDA events around each call,
+    which also keeps a kernel from starting under the tail of the one before: a diagnosis, not
+    the speed of the product path). The role of the reference's ``TTimedBackend``
+    (``demos/infer/llm-bench.lpr:58-236``).
+
+        with Timing() as t:
+            engine.step(...)
+        t.shares()   # {"products": ms, "attention": ms, ...}, after a synchronize
+
+    The time between the end of one call and the start of the next (the host preparing the
+    next launch, other work on the stream) is booked as ``between``, so that the classes add
+    up to the time from the first call to the last.
+    """
+    current: Optional["Timing"] = None
+
+    def __init__(self):
+        self.events = []
+
+    def __enter__(self):
+        Timing.current = self
+        return self
+
+    def __exit__(self, *exc):
+        Timing.current = None
+
+    def shares(self, start=None, end=None) -> dict:
+        """``start``, ``end``: events recorded before the first and after the last call, whose
+        distance to them is booked as ``between`` too."""
+        torch.cuda.synchronize()
+        out: dict = {}
+        last = start
+        for name, e0, e1 in self.events:
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+            if last is not None:
+                out["between"] = out.get("between", 0.0) + last.elapsed_time(e0)
+            last = e1
+        if end is not None and last is not None:
+            out["between"] = out.get("between", 0.0) + last.elapsed_time(end)
+        return out
+
+
 def _call(libname: str, fn: str, argtypes, *args, launches: int = 1) -> None:
     lib = build.load_library(libname)
     f = getattr(lib, fn)
     if f.argtypes is None:
         f.argtypes = argtypes
         f.restype = _i
+    timing = Timing.current
+    if timing is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     rc = f(*args)
     if rc != 0:
         raise KernelError(lib.mb_last_error().decode(errors="replace"))
+    if timing is not None:
+        e1.record()
+        timing.events.append((CLASS_OF.get(fn, "other"), e0, e1))
     Launches.count += launches
 
 
@@ -247,6 +305,16 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, add: bool,
     lib = build.load_library("gemm_tc")
     Launches.count += lib.mb_gemm_tc_last_launches() - 1
     return lib.mb_gemm_tc_last_splits()
+
+
+def wait_selftest(error: torch.Tensor, code: int, tries: int = 2048) -> bool:
+    """Runs one bounded wait that nothing ends (a barrier without anyone to arrive at it),
+    with a limit of ``tries`` polls. True if the wait gave up, as it must; ``error`` (int32
+    device word) then holds ``code``. The kernel returns by itself either way."""
+    gave_up = torch.zeros(1, dtype=torch.int32, device=error.device)
+    _call("gemm_tc", "mb_wait_selftest", [_vp, _i, _c.c_uint, _vp, _vp],
+          _ptr(error), code, tries, _ptr(gave_up), _stream())
+    return bool(gave_up.item())
 
 
 def advance_decode(tok_ids: torch.Tensor, tok_pos: torch.Tensor, chosen: torch.Tensor,

@@ -63,6 +63,12 @@ class GqaAttention(Part):
             self.qkv = Linear(torch.cat([wq, wk, wv], dim=0), rt)
             self.q_only = Linear(self.qkv.weight[:self.qw], rt)
             self.split = None
+            if getattr(rt, "consume_weights", False):
+                # the engine owns the tensors: the three originals go as soon as they are fused,
+                # so that loading never holds much more than the model
+                del wq, wk, wv
+                for key in ("q", "k", "v"):
+                    weights.pop(n[key], None)
         else:
             self.qkv = None
             self.split = [Linear(wq, rt), Linear(wk, rt), Linear(wv, rt)]

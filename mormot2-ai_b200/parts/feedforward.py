@@ -35,6 +35,10 @@ class SwiGluFfn(Part):
             g, u = g.float(), u.float()
         pairs = torch.stack([g, u], dim=1).reshape(2 * self.inter, self.hidden)
         self.gate_up = Linear(pairs, rt, swiglu=True)
+        if getattr(rt, "consume_weights", False):   # the originals go once they are interleaved
+            del g, u
+            weights.pop(n["gate"], None)
+            weights.pop(n["up"], None)
         self.down = Linear(weights[n["down"]], rt)
 
     def forward(self, h, x, step):

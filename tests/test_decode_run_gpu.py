@@ -11,6 +11,7 @@ import torch
 
 from mormot2_ai_b200 import CacheError, Engine, Entry, InferError, Sampling
 from mormot2_ai_b200.sampling import DeviceSampler
+from tests.conftest import close
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
@@ -89,7 +90,6 @@ def test_decode_run_against_the_plain_implementation(tiny, dtype, batch, tempera
     ids = list(prompts[b]) + [firsts[b]] + [r[b] for r in rows]
     if len(ids) <= tiny.config.max_position_embeddings:
         out = eng.step([Entry(slots[b], [ids[-1]])]).cpu().numpy()
-        from tests.conftest import close
         ok, err = close(out, tiny.reference(ids)[-1:], dtype)
         assert ok, err
     for s in slots:
@@ -151,7 +151,6 @@ def test_a_sequence_keeps_fewer_steps_than_were_launched(tiny_a_model):
         run.finish([7, 6, 6])
     run.finish([6, 2, 0])                        # the second keeps two steps, the third none
     assert [eng.length(s) for s in slots] == [62 + 6, 9 + 2, 30]
-    from tests.conftest import close
     for b, keep in enumerate([6, 2, 0]):
         fed = [firsts[b]] + [r[b] for r in rows]
         ids = list(prompts[b]) + fed[:keep] + [5]
@@ -195,17 +194,18 @@ def test_batch_64_at_the_sizes_of_a_real_model():
         part = slice(b0, b0 + 16)
         a = fast.step([Entry(s, p) for s, p in zip(sf[part], prompts[part])])
         b = slow.step([Entry(s, p) for s, p in zip(ss[part], prompts[part])])
-        rel = float((a - b).abs().max() / b.abs().max())
-        assert rel <= 3e-2, ("prompts", b0, rel)
+        ok, err = close(a.cpu().numpy(), b.cpu().numpy(), "bfloat16")
+        assert ok, ("prompts", b0, err)
         tokens = b.argmax(dim=1).tolist() if b0 == 0 else tokens + b.argmax(dim=1).tolist()
     worst = 0.0
     for step in range(4):
         a = fast.step([Entry(s, [t]) for s, t in zip(sf, tokens)])
         b = slow.step([Entry(s, [t]) for s, t in zip(ss, tokens)])
         assert float(b.abs().max()) > 0.5
-        rel = (a - b).abs().amax(dim=1) / b.abs().amax(dim=1)
-        worst = max(worst, float(rel.max()))
-        assert float(rel.max()) <= 3e-2, (step, int(rel.argmax()), float(rel.max()))
+        for i in range(64):                    # every sequence's row in the common measure
+            ok, err = close(a[i].cpu().numpy(), b[i].cpu().numpy(), "bfloat16")
+            assert ok, (step, i, err)
+            worst = max(worst, err)
         tokens = b.argmax(dim=1).tolist()
     # and on the device: the run's greedy picks are the 32-bit path's, or near ties of it
     sampler = DeviceSampler(fast.rt.device, 64, cfg.vocab_size)
@@ -217,7 +217,7 @@ def test_batch_64_at_the_sizes_of_a_real_model():
         top = b.topk(2, dim=1)
         for i, (p, ids, vals) in enumerate(zip(picks, top.indices.tolist(), top.values.tolist())):
             if p != ids[0]:
-                assert float(b[i, ids[0]] - b[i, p]) < 3e-2 * float(b[i].abs().max()), (step, i)
+                assert float(b[i, ids[0]] - b[i, p]) < 6e-2 * float(b[i].std()), (step, i)
         tokens = picks
     run.finish()
     fast.rt.check()

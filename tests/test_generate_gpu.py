@@ -85,6 +85,52 @@ def test_seeded_sampling_repeats_and_differs(tiny_b_model):
     assert alone[0] == want
 
 
+def test_a_kernels_error_word_ends_generation_and_leaves_nothing_held(tiny_a_model):
+    """A kernel whose bounded wait ran out writes a code into the runtime's error word. The
+    failure is made on the host here (the code is written into the word, no kernel is made to
+    wait): ``check`` and ``read_tokens`` raise and clear the word; in the generation loop the
+    code arrives with a step's picks, the loop raises, and no slot, page or run stays open."""
+    from mormot2_ai_b200 import KernelError
+    from mormot2_ai_b200.engine.generate import EngineStepper, Request, generate
+    from mormot2_ai_b200.sampling import Sampling
+    tiny = tiny_a_model
+    client = LlmClient(tiny.folder, dtype="bfloat16", max_batch=3, cache_tokens=1024)
+    eng, rt = client.engine, client.engine.rt
+    rt.error_word.fill_(2)
+    with pytest.raises(KernelError, match="code 2"):
+        rt.check()
+    assert int(rt.error_word.item()) == 0
+    rt.check()
+    rt.error_word.fill_(9)
+    with pytest.raises(KernelError, match="code 9"):
+        rt.read_tokens(2)
+    assert int(rt.error_word.item()) == 0
+    prompts = [tiny.tokens(n, seed=950 + n) for n in (4, 70, 9)]
+    good = client.generate(prompts, max_tokens=12, temperature=0.0, stop=[])
+
+    class Faulty(EngineStepper):
+        launches = 0
+
+        def decode(self, members):
+            run = super().decode(members)
+            launch = run.launch
+
+            def faulty_launch():
+                launch()
+                Faulty.launches += 1
+                if Faulty.launches == 5:
+                    rt.error_word.fill_(3)     # as a kernel of the fifth step would
+            run.launch = faulty_launch
+            return run
+
+    with pytest.raises(KernelError, match="code 3"):
+        generate(Faulty(eng, Sampling(), None, 3), [Request(p, 12) for p in prompts])
+    assert eng.run is None and eng.book.slots.free == eng.max_slots
+    assert all(eng.book.held_pages(g) == 0 for g in range(len(eng.plans)))
+    assert int(rt.error_word.item()) == 0
+    assert client.generate(prompts, max_tokens=12, temperature=0.0, stop=[]) == good
+
+
 def test_command_line(tiny_a_model):
     tiny = tiny_a_model
     env = dict(os.environ)
@@ -99,3 +145,8 @@ def test_command_line(tiny_a_model):
                         "20", "4", "bf16"], capture_output=True, text=True, timeout=600, env=env)
     assert p.returncode == 0, p.stderr[-2000:]
     assert "prefill: 20 tokens" in p.stdout and "decode: 3 tokens" in p.stdout
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llm-bench"), tiny.folder,
+                        "20", "4", "bf16", "--shares"], capture_output=True, text=True,
+                       timeout=600, env=env)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert "products" in p.stdout and "attention" in p.stdout and "decode, mean of 4" in p.stdout

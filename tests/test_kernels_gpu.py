@@ -536,3 +536,21 @@ def test_prefill_attention_of_long_unequal_prompts(window, kind):
                                        hd, p + i, window, scale)
             assert rel(got[row + i], want) <= 1.2e-2, (window, p, i)
         row += n
+
+
+def test_a_wait_that_nothing_ends_gives_up_and_reports(rt):
+    """Every wait of the kernels has an iteration limit, after which the kernel records a code
+    in the runtime's error word and goes on to its end. Here the limit is short (2,048 polls of
+    a barrier that nothing completes): the kernel returns, the code is in the word, the
+    runtime raises it and clears it, and the next kernels run as always."""
+    from mormot2_ai_b200 import KernelError
+    assert K.wait_selftest(rt.error_word, 17, tries=2048)
+    with pytest.raises(KernelError, match="code 17"):
+        rt.check()
+    rt.check()                                                    # cleared
+    a = torch.randn(8, 64).to(torch.bfloat16).to(DEV)
+    w = torch.randn(24, 64).to(torch.bfloat16).to(DEV)
+    c = torch.empty(8, 24, dtype=torch.float32, device=DEV)
+    K.gemm_tc(a, w, c, False, rt.workspace, rt.error_word, rt.sms)
+    assert rel(c.cpu(), a.double().cpu() @ w.double().cpu().T) <= 2e-5
+    rt.check()

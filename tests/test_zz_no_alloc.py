@@ -1,8 +1,8 @@
 """The entry point that allocates nothing (csrc/no_alloc.h), called through its exported C
 symbol as a host without an allocator would call it, against the existing entry point that
-takes the caller's scratch: two calls in a row with different inputs (the second must not see
-what the first left in the shared scratch), and the refusal beyond its limit. This file is
-named to be collected last."""
+takes the caller's scratch and against a float64 restatement of attention: two calls in a row
+with different inputs (the second must not see what the first left in the shared scratch),
+and the refusal beyond its limit. This file is named to be collected last."""
 import ctypes
 import math
 
@@ -38,15 +38,31 @@ def call_static(fn, q, out, step, line, nh, nkv, hd, window, scale, splits):
 
 
 def case(seed, lens, nh, nkv, hd, window):
+    """A cache line, a decode step of one token per sequence, the queries, and what went into
+    the cache (rounded to bfloat16 as the cache holds it)."""
     rng = np.random.default_rng(seed)
     line = make_line(len(lens), 640, nkv, hd, torch.bfloat16, window=window, seed=seed)
+    kv = []
     for slot, n in enumerate(lens):
-        k = torch.tensor(rng.standard_normal((n, nkv, hd)), dtype=torch.float32)
-        v = torch.tensor(rng.standard_normal((n, nkv, hd)), dtype=torch.float32)
+        k = torch.tensor(rng.standard_normal((n, nkv, hd)), dtype=torch.float32).bfloat16().float()
+        v = torch.tensor(rng.standard_normal((n, nkv, hd)), dtype=torch.float32).bfloat16().float()
         fill_line(line, slot, k, v)
+        kv.append((k.numpy(), v.numpy()))
     step = make_step([(slot, n - 1, [0], []) for slot, n in enumerate(lens)])
     q = torch.tensor(rng.standard_normal((len(lens), nh * hd)), dtype=torch.float32)
-    return line, step, q.bfloat16().to(DEV)
+    return line, step, q.bfloat16().to(DEV), kv
+
+
+def attention_in_float64(q, keys, values, nh, nkv, hd, pos, window, scale):
+    """One query row at position pos over keys[0..pos], or the last `window` of them."""
+    lo = max(0, pos + 1 - window) if window else 0
+    out = np.zeros((nh, hd))
+    for h in range(nh):
+        g = h // (nh // nkv)
+        s = keys[lo:pos + 1, g].astype(np.float64) @ q[h].astype(np.float64) * scale
+        p = np.exp(s - s.max())
+        out[h] = (p @ values[lo:pos + 1, g].astype(np.float64)) / p.sum()
+    return out
 
 
 def test_two_calls_in_a_row_equal_the_existing_entry_point():
@@ -55,7 +71,7 @@ def test_two_calls_in_a_row_equal_the_existing_entry_point():
     scale = 1 / math.sqrt(hd)
     before = torch.cuda.memory_allocated()
     for seed, lens, window, splits in ((1, [600, 3, 129], 0, 4), (2, [64, 500], 90, 10)):
-        line, step, q = case(seed, lens, nh, nkv, hd, window)
+        line, step, q, kv = case(seed, lens, nh, nkv, hd, window)
         want = torch.empty(len(lens), nh * hd, dtype=torch.bfloat16, device=DEV)
         scratch = torch.empty(len(lens) * nh * splits * (hd + 2), device=DEV)
         K.attention_decode(q, nh * hd, want, step, line, nh, nkv, hd, window, scale, splits,
@@ -69,12 +85,19 @@ def test_two_calls_in_a_row_equal_the_existing_entry_point():
         err = (got.float() - want.float()).abs().max().item()
         assert err <= 1.2e-2 * max(1.0, want.float().abs().max().item()), err
         assert torch.equal(got, want)        # the same kernels on the same inputs
+        # and both against attention restated in float64 on what the cache holds
+        qf = q.float().cpu().numpy().reshape(len(lens), nh, hd)
+        plain = np.stack([attention_in_float64(qf[b], kv[b][0], kv[b][1], nh, nkv, hd, n - 1,
+                                               window, scale).reshape(-1)
+                          for b, n in enumerate(lens)])
+        err = np.abs(got.float().cpu().numpy() - plain).max()
+        assert err <= 1.2e-2 * max(1.0, np.abs(plain).max()), err
 
 
 def test_sizes_beyond_the_limit_are_refused():
     lib, fn = static_entry()
     nh, nkv, hd = 32, 8, 128
-    line, step, q = case(3, [10] * 64, nh, nkv, hd, 0)
+    line, step, q, _ = case(3, [10] * 64, nh, nkv, hd, 0)
     out = torch.full((64, nh * hd), 3.0, dtype=torch.bfloat16, device=DEV)
     assert 64 * nh * 16 * (hd + 2) > LIMIT
     rc = call_static(fn, q, out, step, line, nh, nkv, hd, 0, 0.1, 16)
