@@ -9,10 +9,11 @@ path); the reference keeps half floats or floats (``model.qwen3.cuda.pas:907-937
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 
+from .guards import Guards, alloc
 from .pages import PAGE, CacheBook, GroupPlan
 
 
@@ -31,16 +32,19 @@ class CacheLine:
 
 class CacheStorage:
     def __init__(self, plans: List[GroupPlan], max_slots: int, dtype: torch.dtype,
-                 device: torch.device, state_needs: Dict[int, "StateNeed"]):
+                 device: torch.device, state_needs: Dict[int, "StateNeed"],
+                 guards: Optional[Guards] = None):
         self.plans = plans
         self.pools: List[torch.Tensor] = []
         self.tables: List[torch.Tensor] = []
         self.tables_host: List[torch.Tensor] = []
         self.lines: Dict[int, CacheLine] = {}
-        for plan in plans:
-            pool = torch.zeros((len(plan.lines), 2, plan.n_pages, plan.kv_heads, PAGE,
-                                plan.head_dim), dtype=dtype, device=device)
-            table = torch.zeros((max_slots, plan.max_pages), dtype=torch.int32, device=device)
+        for g, plan in enumerate(plans):
+            pool = alloc(guards, f"keys and values of group {g}",
+                         (len(plan.lines), 2, plan.n_pages, plan.kv_heads, PAGE, plan.head_dim),
+                         dtype, device)
+            table = alloc(guards, f"page table of group {g}", (max_slots, plan.max_pages),
+                          torch.int32, device)
             # pageable on purpose: the copy to the device then reads it before returning, so the
             # host may change it again at once
             host = torch.zeros((max_slots, plan.max_pages), dtype=torch.int32)
@@ -56,8 +60,8 @@ class CacheStorage:
         # that fails half way leaves the state it found
         self.state_init: Dict[int, float] = {l: float(n.init) for l, n in state_needs.items()}
         self.states: Dict[int, torch.Tensor] = {
-            line: torch.full((max_slots,) + tuple(n.shape), float(n.init),
-                             dtype=getattr(torch, n.dtype), device=device)
+            line: alloc(guards, f"state of line {line}", (max_slots,) + tuple(n.shape),
+                        getattr(torch, n.dtype), device, float(n.init))
             for line, n in state_needs.items()}
         self.saved: Dict[int, torch.Tensor] = {l: torch.empty_like(s)
                                                for l, s in self.states.items()}
@@ -77,6 +81,25 @@ class CacheStorage:
                 host[slot, entry] = page
                 lo, hi = min(lo, slot), max(hi, slot)
             self.tables[g][lo:hi + 1].copy_(host[lo:hi + 1])
+
+    def table_faults(self, book: CacheBook) -> List[str]:
+        """Compares the page tables on the device with the bookkeeping: every entry that a
+        sequence holds must name the page the book gave it, and no page may be held twice.
+        Returns what is wrong (nothing, when all is well)."""
+        out = []
+        for g, table in enumerate(self.tables):
+            dev = table.cpu()
+            seen: Dict[int, int] = {}
+            for slot in range(dev.shape[0]):
+                for entry, page in enumerate(book.pages[g][slot]):
+                    if int(dev[slot, entry]) != page:
+                        out.append(f"group {g}, slot {slot}, entry {entry}: the device table "
+                                   f"names page {int(dev[slot, entry])}, the book page {page}")
+                    if page in seen:
+                        out.append(f"group {g}: page {page} is held by slots {seen[page]} "
+                                   f"and {slot}")
+                    seen[page] = slot
+        return out
 
     def reset_state(self, slot: int) -> None:
         for line, s in self.states.items():

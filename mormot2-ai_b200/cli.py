@@ -52,8 +52,11 @@ def llm_bench(argv: List[str]) -> int:
     eng = Engine.from_folder(a.folder, dtype=_dtype(a.weights), max_tokens=total,
                              max_slots=a.batch)
     c = eng.config
+    st = eng.stats()
     print(f"loaded in {int((time.time() - t0) * 1000)} ms: {c.num_hidden_layers} layers, "
-          f"hidden {c.hidden_size}, vocab {c.vocab_size}, weights {a.weights}")
+          f"hidden {c.hidden_size}, vocab {c.vocab_size}, weights {a.weights}; on the device "
+          f"{st['device_bytes'] / 2**20:.0f} MiB, of which cache {st['cache_bytes'] / 2**20:.0f} MiB "
+          f"({st['slots']} slots, {sum(st['pages'])} pages of 64 positions)")
     gen = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, c.vocab_size, (a.prompt_tokens,), generator=gen).tolist()
                for _ in range(a.batch)]
@@ -75,6 +78,9 @@ def llm_bench(argv: List[str]) -> int:
     if a.new_tokens > 1:
         print(f"decode: {a.batch * (a.new_tokens - 1)} tokens in {int((t2 - t1) * 1000)} ms = "
               f"{a.batch * (a.new_tokens - 1) / (t2 - t1):.1f} tokens/s")
+    st = eng.stats()
+    print(f"passes of the model: {st['passes']}, kernel launches: {st['kernel_launches']}, "
+          f"decode graphs: {st['decode_graphs']}, pages held: {sum(st['pages_held'])}")
     if a.shares:
         for s in slots:
             eng.truncate(s, 0)

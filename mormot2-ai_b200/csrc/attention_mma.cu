@@ -179,7 +179,10 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
       int mine = 0;
       if (i0 + lane < n_pages) {
         const int p = p_first + (i0 + lane) * S;
-        mine = page_table[(size_t)slot * max_pages + (ring_pages > 0 ? p % ring_pages : p)];
+        const int entry = ring_pages > 0 ? p % ring_pages : p;
+        mine = MB_INDEX_OK(entry < max_pages, 1, slot, p, max_pages)
+                   ? page_table[(size_t)slot * max_pages + entry] : 0;
+        if (!MB_INDEX_OK(mine >= 0, 2, slot, entry, mine)) mine = 0;
       }
       const int n = min(32, n_pages - i0);
       for (int i = 0; i < n; ++i) {
@@ -607,7 +610,10 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
   auto issue = [&](int i) {  // page i of the CTA into stage i % PRE_STAGES
     if (i < n_pages) {
       const int p = page0 + i;
-      const int page = page_table[(size_t)slot * max_pages + (ring_pages > 0 ? p % ring_pages : p)];
+      const int entry = ring_pages > 0 ? p % ring_pages : p;
+      int page = MB_INDEX_OK(entry < max_pages, 1, slot, p, max_pages)
+                     ? page_table[(size_t)slot * max_pages + entry] : 0;
+      if (!MB_INDEX_OK(page >= 0, 2, slot, entry, page)) page = 0;
       const bf16* ksrc = kpool + ((size_t)page * nkv + g) * MB_PAGE * HD;
       const bf16* vsrc = vpool + ((size_t)page * nkv + g) * MB_PAGE * HD;
       const uint32_t kd = tiles + (i % PRE_STAGES) * STAGE, vd = kd + MB_PAGE * KP;

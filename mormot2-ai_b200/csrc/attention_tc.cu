@@ -218,8 +218,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
       // the first products run two pages ahead of the second ones: so do the loads of K
       auto row_of = [&](int j) {
         const int p = page0 + j;
-        const int page =
-            page_table[(size_t)slot_of_seq * max_pages + (ring_pages > 0 ? p % ring_pages : p)];
+        const int entry = ring_pages > 0 ? p % ring_pages : p;
+        int page = MB_INDEX_OK(entry < max_pages, 1, slot_of_seq, p, max_pages)
+                       ? page_table[(size_t)slot_of_seq * max_pages + entry] : 0;
+        if (!MB_INDEX_OK(page >= 0, 2, slot_of_seq, entry, page)) page = 0;
         return (page * nkv + g) * MB_PAGE;
       };
       auto load_k = [&](int j) {

@@ -31,6 +31,11 @@ NVCC_FLAGS = [
 # more flags for nvcc, e.g. MORMOT_B200_NVCC_FLAGS="-DMB_WAIT_LIMIT=1024" (the iteration limit of
 # the kernels' bounded waits); they are part of the built library's name
 NVCC_FLAGS += os.environ.get("MORMOT_B200_NVCC_FLAGS", "").split()
+# MORMOT_B200_DEBUG=1: the build whose kernels check every index into a page table before they
+# use it (csrc/common.cuh); Runtime.check then also asks every library for what it found
+DEBUG_BOUNDS = os.environ.get("MORMOT_B200_DEBUG", "") not in ("", "0")
+if DEBUG_BOUNDS:
+    NVCC_FLAGS.append("-DMB_DEBUG_BOUNDS")
 
 # library name -> source file; headers that every library depends on
 SOURCES = {
@@ -90,14 +95,18 @@ def _find_build_dir() -> str:
 
 
 def _digest(name: str) -> str:
+    """Names a build: the sources' digest, then the flags' digest."""
     h = hashlib.sha256()
     for fn in [SOURCES[name]] + HEADERS + EXTRA_HEADERS.get(name, []):
         path = os.path.join(HERE, fn)
         if os.path.isfile(path):
             with open(path, "rb") as f:
                 h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
-    return h.hexdigest()[:16]
+    return h.hexdigest()[:16] + "-" + _flags_digest()
+
+
+def _flags_digest() -> str:
+    return hashlib.sha256(" ".join(NVCC_FLAGS).encode()).hexdigest()[:6]
 
 
 def library_path(name: str) -> str:
@@ -138,10 +147,11 @@ def compile_library(name: str, verbose: bool = True) -> str:
             pass
         raise KernelError(f"nvcc failed on {SOURCES[name]}:\n{log.decode(errors='replace')}")
     os.replace(tmp, out)
-    # builds of older sources of this library are of no use any more
-    prefix = f"libmb_{name}-"
+    # builds of older sources of this library with the same flags are of no use any more (a
+    # build with other flags, the debug build for one, stays beside this one)
+    prefix, suffix = f"libmb_{name}-", f"-{_flags_digest()}.so"
     for fn in os.listdir(os.path.dirname(out)):
-        if fn.startswith(prefix) and fn.endswith(".so") and fn != os.path.basename(out):
+        if fn.startswith(prefix) and fn.endswith(suffix) and fn != os.path.basename(out):
             try:
                 os.unlink(os.path.join(os.path.dirname(out), fn))
             except OSError:
@@ -189,6 +199,24 @@ def load_library(name: str) -> ctypes.CDLL:
             lib.mb_last_error.restype = ctypes.c_char_p
             _loaded[name] = lib
         return _loaded[name]
+
+
+def debug_faults() -> List[str]:
+    """What the loaded libraries of a debug build found since the last call (and forgets it):
+    one line per library whose kernels met an index outside its table."""
+    if not DEBUG_BOUNDS:
+        return []
+    with _lock:
+        libs = dict(_loaded)
+    out = []
+    names = {1: "a position outside the slot's row of the page table", 2: "a negative page"}
+    for name, lib in libs.items():
+        four = (ctypes.c_int * 4)()
+        rc = lib.mb_debug_fault(four)
+        if rc == 1 and four[0]:
+            out.append(f"{name}: {names.get(four[0], 'code %d' % four[0])} "
+                       f"({four[1]}, {four[2]}, {four[3]})")
+    return out
 
 
 def build_all(verbose: bool = True) -> List[str]:

@@ -80,8 +80,40 @@ static cudaError_t mb_launch_clusters(void (*kernel)(KArgs...), dim3 grid, dim3 
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
-#define MB_DEFINE_LAST_ERROR \
-  MB_EXPORT const char* mb_last_error() { return g_mb_error; }
+// Debug builds (-DMB_DEBUG_BOUNDS, what MORMOT_B200_DEBUG=1 asks of the build): every lookup in
+// a page table checks its index and the page it finds before it uses them. The first
+// violation of a library is kept in a device word with three numbers that describe it, the
+// access goes to row 0 of the pool instead (a place that exists), and the host reads the word
+// with mb_debug_fault() (Runtime.check does). This stands in for a memory checker where none
+// can be run. Codes: 1 a position outside the slot's table row, 2 a negative page.
+#ifdef MB_DEBUG_BOUNDS
+__device__ int g_mb_debug_fault[4];
+__device__ __forceinline__ bool mb_index_ok(bool ok, int code, int a, int b, int c) {
+  if (!ok && atomicCAS(&g_mb_debug_fault[0], 0, code) == 0) {
+    g_mb_debug_fault[1] = a;
+    g_mb_debug_fault[2] = b;
+    g_mb_debug_fault[3] = c;
+  }
+  return ok;
+}
+#define MB_INDEX_OK(cond, code, a, b, c) mb_index_ok((cond), (code), (a), (b), (c))
+#define MB_DEFINE_DEBUG_FAULT                                                          \
+  MB_EXPORT int mb_debug_fault(int* out4) {                                            \
+    const int zero[4] = {0, 0, 0, 0};                                                  \
+    if (cudaMemcpyFromSymbol(out4, g_mb_debug_fault, sizeof(zero)) != cudaSuccess) return -2; \
+    if (out4[0] && cudaMemcpyToSymbol(g_mb_debug_fault, zero, sizeof(zero)) != cudaSuccess)   \
+      return -2;                                                                       \
+    return 1;                                                                          \
+  }
+#else
+#define MB_INDEX_OK(cond, code, a, b, c) true
+#define MB_DEFINE_DEBUG_FAULT \
+  MB_EXPORT int mb_debug_fault(int*) { return 0; } /* 0: not a debug build */
+#endif
+
+#define MB_DEFINE_LAST_ERROR                                       \
+  MB_EXPORT const char* mb_last_error() { return g_mb_error; }    \
+  MB_DEFINE_DEBUG_FAULT
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
@@ -127,6 +159,8 @@ __device__ __forceinline__ size_t kv_row(const int* __restrict__ page_table, int
                                          int ring_pages, int slot, int pos, int kv_heads, int g) {
   int lp = pos / MB_PAGE;
   if (ring_pages > 0) lp %= ring_pages;
+  if (!MB_INDEX_OK(pos >= 0 && slot >= 0 && lp < max_pages, 1, slot, pos, max_pages)) return 0;
   const int page = page_table[(size_t)slot * max_pages + lp];
+  if (!MB_INDEX_OK(page >= 0, 2, slot, lp, page)) return 0;
   return ((size_t)page * kv_heads + g) * MB_PAGE + (pos % MB_PAGE);
 }

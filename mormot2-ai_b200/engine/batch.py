@@ -41,12 +41,13 @@ class StepContext:
 class StepBuffers:
     """Pinned host and device index buffers, reused by every pass."""
 
-    def __init__(self, max_tokens: int, max_seqs: int, device: torch.device):
+    def __init__(self, max_tokens: int, max_seqs: int, device: torch.device, guards=None):
         self.max_tokens, self.max_seqs = max_tokens, max_seqs
         self.size = 5 * max_tokens + 3 * max_seqs + 1
         self.host = torch.zeros(self.size, dtype=torch.int32).pin_memory()
         self.host_np = self.host.numpy()      # the same pinned memory, for vectorised filling
-        self.dev = torch.zeros(self.size, dtype=torch.int32, device=device)
+        from ..cache.guards import alloc
+        self.dev = alloc(guards, "step index arrays", (self.size,), torch.int32, device)
         self.copied = torch.cuda.Event()
         self.in_flight = False
         self.views = {}

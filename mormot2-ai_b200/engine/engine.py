@@ -18,6 +18,7 @@ import numpy as np
 import torch
 
 from .. import kernels as K
+from ..cache.guards import Guards
 from ..cache.pages import PAGE, CacheBook, pages_for, plan_groups
 from ..cache.storage import CacheStorage
 from ..config.registry import config_of_folder
@@ -80,7 +81,7 @@ class Engine:
                                  self.prefill_chunk)
         self.book = CacheBook(self.plans, self.max_slots, self.max_context)
         self.cache = CacheStorage(self.plans, self.max_slots, rt.dtype, rt.device,
-                                  self.model.state_needs)
+                                  self.model.state_needs, rt.guards)
         # whether a slot's fixed-size state holds exactly the slot's length (the reference's
         # fStateOk, decoder.pas:436, :3301, :3348); only models with such state look at it
         self.has_state = bool(self.model.state_needs)
@@ -89,7 +90,7 @@ class Engine:
         # decoder.pas:412-421, Common :1264-1273)
         self.ids: List[List[int]] = [[] for _ in range(self.max_slots)]
         self.run: Optional[DecodeRun] = None             # the decode run that is open, if any
-        self.buffers = StepBuffers(self.max_step_tokens, self.max_slots, rt.device)
+        self.buffers = StepBuffers(self.max_step_tokens, self.max_slots, rt.device, rt.guards)
         self.on_state: Optional[Callable[[str, torch.Tensor], None]] = None
         self.passes = 0  # passes of the model so far (a step of long prompts takes several)
         self.last_slots: Optional[torch.Tensor] = None   # slots of the last step, on the device
@@ -107,7 +108,8 @@ class Engine:
         if dtype not in DTYPES:
             raise InferError(f"dtype \"{dtype}\" is not bfloat16 or float32")
         config = config_of_folder(folder)
-        rt = Runtime(DTYPES[dtype], device, kwargs.pop("fast_kernels", True))
+        rt = Runtime(DTYPES[dtype], device, kwargs.pop("fast_kernels", True),
+                     Guards() if kwargs.pop("guard", False) else None)
         model = DecoderModel(config.to_model_spec())
         weights = bind_tensors(model.tensors(), SafeTensorsFolder(folder), rt.dtype, rt.device)
         rt.consume_weights = True
@@ -118,7 +120,8 @@ class Engine:
                     std: float = 0.02, norm_std: float = 0.1, **kwargs) -> "Engine":
         """Random weights drawn on the device (for shapes too large to write to a folder)."""
         from ..weights.random_init import random_tensors
-        rt = Runtime(DTYPES[dtype], device, kwargs.pop("fast_kernels", True))
+        rt = Runtime(DTYPES[dtype], device, kwargs.pop("fast_kernels", True),
+                     Guards() if kwargs.pop("guard", False) else None)
         model = DecoderModel(config.to_model_spec())
         weights = random_tensors(model.tensors(), seed, std, norm_std, rt.dtype, device)
         rt.consume_weights = True
@@ -190,6 +193,30 @@ class Engine:
     def length(self, slot: int) -> int:
         self.book.check_open(slot)
         return self.book.length[slot]
+
+    def faults(self) -> List[str]:
+        """Checks that stand in for a memory checker, for tests and debugging (they read the
+        device): buffers whose guard bands a kernel damaged (engines made with ``guard=True``)
+        and page tables that differ from the bookkeeping. Empty when all is well."""
+        torch.cuda.synchronize(self.rt.device)
+        found = self.rt.guards.damaged() if self.rt.guards is not None else []
+        return found + self.cache.table_faults(self.book)
+
+    def stats(self) -> Dict[str, object]:
+        """Counters and sizes for logs: passes of the model and kernel launches so far, the
+        bytes of the cache's pools and of everything this process holds on the device, slots
+        and pages in use per group of cache lines, decode graphs kept."""
+        return {
+            "passes": self.passes,
+            "kernel_launches": K.Launches.count,
+            "cache_bytes": self.cache.bytes(),
+            "device_bytes": int(torch.cuda.memory_allocated(self.rt.device)),
+            "slots_open": self.max_slots - self.book.slots.free,
+            "slots": self.max_slots,
+            "pages_held": [self.book.held_pages(g) for g in range(len(self.plans))],
+            "pages": [p.n_pages for p in self.plans],
+            "decode_graphs": len(self.graphs),
+        }
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[Entry]) -> Optional[torch.Tensor]:

@@ -14,10 +14,15 @@ MAIL_RING = 4          # copies of the mailbox that may be on their way to the h
 
 
 class Runtime:
-    def __init__(self, dtype: torch.dtype, device: str = "cuda:0", fast_kernels: bool = True):
+    def __init__(self, dtype: torch.dtype, device: str = "cuda:0", fast_kernels: bool = True,
+                 guards=None):
+        """``guards``: a ``cache.guards.Guards`` that the buffers of this runtime and of the
+        engine built on it are made through (bands around each that a stray write damages)."""
         if dtype not in (torch.float32, torch.bfloat16):
             raise KernelError(f"activations of {dtype} are not supported (bfloat16 or float32)")
         K.require_gpu()
+        from ..cache.guards import alloc
+        self.guards = guards
         self.dtype = dtype
         self.device = torch.device(device)
         # the tensor-core kernels serve the bfloat16 path only; the 32-bit path multiplies and
@@ -29,14 +34,14 @@ class Runtime:
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         # scratch of the split matrix products (float32) and the word that kernels set when
         # one of their bounded waits ran out
-        self.workspace = (torch.empty(16 << 20, dtype=torch.float32, device=self.device)
-                          if self.fast_kernels else None)
+        self.workspace = (alloc(guards, "split-sum workspace", (16 << 20,), torch.float32,
+                                self.device, None) if self.fast_kernels else None)
         # the partial sums of a split product that its consumer adds up (parts/linear.py)
-        self.pending_buf = (torch.empty(8 << 20, dtype=torch.float32, device=self.device)
-                            if self.fast_kernels else None)
+        self.pending_buf = (alloc(guards, "pending split sums", (8 << 20,), torch.float32,
+                                  self.device, None) if self.fast_kernels else None)
         # word 0: set by a kernel when one of its bounded waits ran out; the words after it: the
         # tokens that the sampler chose in a step, so that one copy brings both to the host
-        self.mailbox = torch.zeros(1 + MAILBOX_TOKENS, dtype=torch.int32, device=self.device)
+        self.mailbox = alloc(guards, "mailbox", (1 + MAILBOX_TOKENS,), torch.int32, self.device)
         self.error_word = self.mailbox[:1]
         self.host_mailbox = torch.zeros(1 + MAILBOX_TOKENS, dtype=torch.int32).pin_memory()
         self.mail_event = torch.cuda.Event()
@@ -45,8 +50,13 @@ class Runtime:
         self.ring_events = [torch.cuda.Event() for _ in range(MAIL_RING)]
 
     def check(self) -> None:
-        """Raises if a kernel recorded that one of its waits ran out (synchronizes)."""
+        """Raises if a kernel recorded that one of its waits ran out (synchronizes); in a debug
+        build (MORMOT_B200_DEBUG=1) also if a kernel met an index outside a page table."""
         self._raise_if(int(self.error_word.item()))
+        from ..csrc import build
+        found = build.debug_faults()
+        if found:
+            raise KernelError("the kernels' index checks: " + "; ".join(found))
 
     def _raise_if(self, code: int) -> None:
         if code:

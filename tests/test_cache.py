@@ -179,3 +179,23 @@ def test_random_walk_loses_nothing():
     for s in list(live):
         b.close(s)
     assert all(b.held_pages(g) == 0 for g in range(len(plans)))       # none lost
+
+
+def test_guard_bands_tell_a_write_outside_a_buffer():
+    import torch
+    from mormot2_ai_b200.cache.guards import BAND_BYTES, Guards, alloc
+    g = Guards()
+    a = g.alloc("a", (3, 5), torch.float32, "cpu")
+    b = g.alloc("b", (7,), torch.int32, "cpu", fill=None)
+    assert a.shape == (3, 5) and float(a.abs().max()) == 0.0 and b.dtype == torch.int32
+    a.fill_(1.5)
+    b.fill_(-1)
+    assert g.damaged() == []                       # writes inside leave the bands alone
+    raw = torch.tensor([], dtype=torch.uint8).set_(a.untyped_storage())
+    assert raw.numel() == 2 * BAND_BYTES + 3 * 5 * 4
+    raw[BAND_BYTES + 3 * 5 * 4] = 0                # the first byte behind a
+    assert g.damaged() == ["a (behind)"]
+    raw_b = torch.tensor([], dtype=torch.uint8).set_(b.untyped_storage())
+    raw_b[BAND_BYTES - 1] = 7                      # the last byte before b
+    assert g.damaged() == ["a (behind)", "b (before)"]
+    assert alloc(None, "c", (2, 2), torch.float32, "cpu", 3.0).tolist() == [[3.0, 3.0]] * 2

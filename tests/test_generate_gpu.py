@@ -145,6 +145,7 @@ def test_command_line(tiny_a_model):
                         "20", "4", "bf16"], capture_output=True, text=True, timeout=600, env=env)
     assert p.returncode == 0, p.stderr[-2000:]
     assert "prefill: 20 tokens" in p.stdout and "decode: 3 tokens" in p.stdout
+    assert "MiB, of which cache" in p.stdout and "kernel launches:" in p.stdout
     p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llm-bench"), tiny.folder,
                         "20", "4", "bf16", "--shares"], capture_output=True, text=True,
                        timeout=600, env=env)

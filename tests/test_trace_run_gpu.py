@@ -16,10 +16,10 @@ pytestmark = pytest.mark.gpu
 TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
 
 
-def replay(model, dtype, steps, out_dir, max_tokens):
+def replay(model, dtype, steps, out_dir, max_tokens, more=()):
     text = "".join(json.dumps(s) + "\n" for s in steps)
     p = subprocess.run([sys.executable, TRACE_RUN, "--model", model, "--dtype", dtype,
-                        "--out", str(out_dir), "--max-tokens", str(max_tokens)],
+                        "--out", str(out_dir), "--max-tokens", str(max_tokens)] + list(more),
                        input=text, capture_output=True, text=True, timeout=900)
     assert p.returncode == 0, p.stderr[-3000:]
     done = [l for l in p.stdout.splitlines() if l.startswith("done ")]
@@ -113,11 +113,23 @@ def test_steps_without_wants_write_nothing(tiny_a_model, tmp_path):
     steps = [{"step": 0, "entries": [{"id": "a", "tokens": ids[:10], "want": []}], "end": []},
              {"step": 1, "entries": [{"id": "a", "tokens": ids[10:], "want": [9]}], "end": ["a"]},
              {"step": 2, "entries": [], "end": []}]
-    replay(tiny.folder, "float32", steps, tmp_path, max_tokens=64)
+    replay(tiny.folder, "float32", steps, tmp_path, max_tokens=64, more=["--manifest"])
     assert not os.path.exists(os.path.join(str(tmp_path), "0.f32"))
     got = logits_of(tmp_path, 1, tiny.config.vocab_size)
     ok, err = close(got, tiny.reference(ids)[-1:], "float32")
     assert ok, err
+    # the same logits in the reference project's fixture format, read as its loader reads it
+    import hashlib
+    manifest = json.load(open(os.path.join(str(tmp_path), "manifest.json")))
+    blob = open(os.path.join(str(tmp_path), manifest["blob"]["file"]), "rb").read()
+    assert hashlib.sha256(blob).hexdigest() == manifest["blob"]["sha256"]
+    assert len(blob) == manifest["blob"]["bytes"]
+    (t,) = manifest["tensors"]
+    assert t["name"] == "step1.logits" and t["dtype"] == "f32"
+    assert t["shape"] == [1, tiny.config.vocab_size] and t["bytes"] == 4 * tiny.config.vocab_size
+    part = blob[t["offset"]:t["offset"] + t["bytes"]]
+    assert hashlib.sha256(part).hexdigest() == t["sha256"]
+    assert np.array_equal(np.frombuffer(part, "<f4").reshape(t["shape"]), got)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
