@@ -36,9 +36,13 @@ class Runtime:
         # one of their bounded waits ran out
         self.workspace = (alloc(guards, "split-sum workspace", (16 << 20,), torch.float32,
                                 self.device, None) if self.fast_kernels else None)
-        # the partial sums of a split product that its consumer adds up (parts/linear.py)
-        self.pending_buf = (alloc(guards, "pending split sums", (8 << 20,), torch.float32,
-                                  self.device, None) if self.fast_kernels else None)
+        # the partial sums of a split product that its consumer adds up (parts/linear.py): two
+        # halves used in turn, so that two products may be pending at once (a block with two
+        # branches that both defer their sums)
+        self.pending_bufs = ([alloc(guards, f"pending split sums {i}", (4 << 20,), torch.float32,
+                                    self.device, None) for i in range(2)]
+                             if self.fast_kernels else None)
+        self.pending_turn = 0
         # word 0: set by a kernel when one of its bounded waits ran out; the words after it: the
         # tokens that the sampler chose in a step, so that one copy brings both to the host
         self.mailbox = alloc(guards, "mailbox", (1 + MAILBOX_TOKENS,), torch.int32, self.device)
@@ -48,6 +52,14 @@ class Runtime:
         # the same for steps that are read a step late (engine/decode.py)
         self.host_ring = torch.zeros((MAIL_RING, 1 + MAILBOX_TOKENS), dtype=torch.int32).pin_memory()
         self.ring_events = [torch.cuda.Event() for _ in range(MAIL_RING)]
+
+    @property
+    def pending_buf(self) -> Optional[torch.Tensor]:
+        """The buffer for the next product's pending sums (the other one than last time)."""
+        if self.pending_bufs is None:
+            return None
+        self.pending_turn ^= 1
+        return self.pending_bufs[self.pending_turn]
 
     def check(self) -> None:
         """Raises if a kernel recorded that one of its waits ran out (synchronizes); in a debug

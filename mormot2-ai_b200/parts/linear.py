@@ -17,8 +17,9 @@ from .. import kernels as K
 class Pending:
     """Partial sums [splits, M, N] (float32) of a product whose K range was split: whoever
     reads the result next adds them up, in split order (an RMSNorm adds them into the residual
-    it norms, the q/k norm kernel adds them as it reads q, k and v). They live in one buffer of
-    the runtime, so at most one product is pending at a time."""
+    it norms, the q/k norm kernel adds them as it reads q, k and v). They live in one of two
+    buffers of the runtime that are used in turn, so at most two products are pending at a
+    time."""
 
     def __init__(self, partial: torch.Tensor):
         self.partial = partial

@@ -29,15 +29,15 @@ class FastLinear:
         rt = self.rt
         M, N = a.shape[0], self.weight.shape[0]
         if (a.dtype != torch.bfloat16 or a.stride(0) % 8 or a.data_ptr() % 16 or M > 64
-                or -(-N // 128) > rt.sms or rt.pending_buf is None):
+                or -(-N // 128) > rt.sms or rt.pending_bufs is None):
             return None
         # c is only written when the kernel does not split after all
         c = torch.empty((M, N), dtype=torch.float32, device=a.device)
-        splits = K.gemm_tc(a, self.weight, c, False, rt.pending_buf, rt.error_word, rt.sms,
-                           defer=True)
+        buf = rt.pending_buf
+        splits = K.gemm_tc(a, self.weight, c, False, buf, rt.error_word, rt.sms, defer=True)
         if splits <= 1:
             return Pending(c.unsqueeze(0))
-        return Pending(rt.pending_buf[:splits * M * N].view(splits, M, N))
+        return Pending(buf[:splits * M * N].view(splits, M, N))
 
     def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor],
                  add_into: Optional[torch.Tensor]) -> bool:
