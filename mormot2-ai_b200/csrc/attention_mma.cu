@@ -127,6 +127,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   constexpr int CH = HD / 32;  // 32-dim chunks of q·k
   constexpr int DB = HD / 64;  // 64-dim blocks of p·v
   constexpr uint32_t TILE = MB_PAGE * HD * 2;  // bytes of a page's keys (or values)
+  MB_TRACE_BEGIN();
   extern __shared__ __align__(128) uint8_t dec_smem[];
   // [stages][K tile | V tile], then the barriers; after the loop the tiles' memory holds the
   // warps' partial results for the merge
@@ -378,6 +379,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     }
     cluster_sync_all();  // no CTA leaves while another may still read its shared memory
   }
+  MB_TRACE_END(4);
 }
 
 // out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), the splits in order

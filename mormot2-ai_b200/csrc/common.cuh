@@ -111,7 +111,48 @@ __device__ __forceinline__ bool mb_index_ok(bool ok, int code, int a, int b, int
   MB_EXPORT int mb_debug_fault(int*) { return 0; } /* 0: not a debug build */
 #endif
 
+// -DMB_TRACE (a probe's build): every CTA of the kernels that carry MB_TRACE_BEGIN / _END leaves
+// its start and end (global nanosecond timer) and the kernel's id in a buffer of the library.
+#ifdef MB_TRACE
+#define MB_TRACE_CAP (1 << 17)
+__device__ unsigned long long g_mb_trace[MB_TRACE_CAP][2];
+__device__ unsigned int g_mb_trace_n;
+__device__ __forceinline__ unsigned long long mb_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define MB_TRACE_BEGIN() const unsigned long long mb_t0_ = mb_now()
+#define MB_TRACE_END(id_)                                                         \
+  do {                                                                            \
+    if (threadIdx.x == 0) {                                                       \
+      const unsigned int i_ = atomicAdd(&g_mb_trace_n, 1u);                       \
+      if (i_ < MB_TRACE_CAP) {                                                    \
+        g_mb_trace[i_][0] = (mb_t0_ & 0x00ffffffffffffffull) | ((unsigned long long)(id_) << 56); \
+        g_mb_trace[i_][1] = mb_now();                                             \
+      }                                                                           \
+    }                                                                             \
+  } while (0)
+#define MB_DEFINE_TRACE                                                           \
+  MB_EXPORT int mb_trace_read(unsigned long long* out, int cap) {                 \
+    unsigned int n = 0;                                                           \
+    cudaDeviceSynchronize();                                                      \
+    cudaMemcpyFromSymbol(&n, g_mb_trace_n, 4);                                    \
+    if ((int)n > cap) n = cap;                                                    \
+    if (n > MB_TRACE_CAP) n = MB_TRACE_CAP;                                       \
+    cudaMemcpyFromSymbol(out, g_mb_trace, (size_t)n * 16);                        \
+    const unsigned int zero = 0;                                                  \
+    cudaMemcpyToSymbol(g_mb_trace_n, &zero, 4);                                   \
+    return (int)n;                                                                \
+  }
+#else
+#define MB_TRACE_BEGIN() do {} while (0)
+#define MB_TRACE_END(id_) do {} while (0)
+#define MB_DEFINE_TRACE
+#endif
+
 #define MB_DEFINE_LAST_ERROR                                       \
+  MB_DEFINE_TRACE                                                  \
   MB_EXPORT const char* mb_last_error() { return g_mb_error; }    \
   MB_DEFINE_DEBUG_FAULT
 

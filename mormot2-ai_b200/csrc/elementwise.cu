@@ -86,18 +86,51 @@ __global__ void __launch_bounds__(RMS_THREADS)
 rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partial, int parts,
                    size_t part_stride, const void* __restrict__ w, int w_bf16, float eps,
                    TO* __restrict__ y, const int* __restrict__ rows, int H) {
-  mb_grid_wait();
-  mb_grid_launch_next();
+  MB_TRACE_BEGIN();
   __shared__ float red[33];
   const int r = blockIdx.x;
+  // Before the wait for the kernel before: what does not depend on it. The row index and the
+  // norm's weights were settled by kernels further back (complete once this kernel runs: every
+  // kernel of the stream waits for the one before it ahead of letting its successor start).
+  // With PARTIAL the kernel before is the matrix product that left its split sums, which
+  // wrote nothing else: the residual row itself can be asked for before the wait too, and
+  // only the split sums come after it.
   const int src = rows ? rows[r] : r;
   float* xr = x + (size_t)src * H;
+  float wv[VEC][4];
+  if (y != nullptr) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = (i * RMS_THREADS + threadIdx.x) * 4;
+      if (c >= H) continue;
+      if (w_bf16) {  // four weights with one load (c is a multiple of 4)
+        const uint2 raw = *(const uint2*)((const __nv_bfloat16*)w + c);
+        const float2 lo = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x);
+        const float2 hi = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+        wv[i][0] = lo.x; wv[i][1] = lo.y; wv[i][2] = hi.x; wv[i][3] = hi.y;
+      } else {
+        const float4 raw = *(const float4*)((const float*)w + c);
+        wv[i][0] = raw.x; wv[i][1] = raw.y; wv[i][2] = raw.z; wv[i][3] = raw.w;
+      }
+    }
+  }
   float4 v[VEC];
   float sum = 0.f;
+  if (PARTIAL) {
 #pragma unroll
-  for (int i = 0; i < VEC; ++i) {
-    const int c = (i * RMS_THREADS + threadIdx.x) * 4;
-    v[i] = c < H ? *(const float4*)(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < VEC; ++i) {
+      const int c = (i * RMS_THREADS + threadIdx.x) * 4;
+      v[i] = c < H ? *(const float4*)(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  mb_grid_wait();
+  mb_grid_launch_next();
+  if (!PARTIAL) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const int c = (i * RMS_THREADS + threadIdx.x) * 4;
+      v[i] = c < H ? *(const float4*)(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
   if (PARTIAL) {  // a kernel of its own: the loads in flight below cost registers
 #pragma unroll
@@ -131,20 +164,11 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partial, int
   for (int i = 0; i < VEC; ++i) {
     const int c = (i * RMS_THREADS + threadIdx.x) * 4;
     if (c >= H) continue;
-    float o[4], wv[4];
-    if (w_bf16) {  // four weights with one load (c is a multiple of 4)
-      const uint2 raw = *(const uint2*)((const __nv_bfloat16*)w + c);
-      const float2 lo = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x);
-      const float2 hi = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
-      wv[0] = lo.x; wv[1] = lo.y; wv[2] = hi.x; wv[3] = hi.y;
-    } else {
-      const float4 raw = *(const float4*)((const float*)w + c);
-      wv[0] = raw.x; wv[1] = raw.y; wv[2] = raw.z; wv[3] = raw.w;
-    }
-    o[0] = wv[0] * (v[i].x * inv);
-    o[1] = wv[1] * (v[i].y * inv);
-    o[2] = wv[2] * (v[i].z * inv);
-    o[3] = wv[3] * (v[i].w * inv);
+    float o[4];
+    o[0] = wv[i][0] * (v[i].x * inv);
+    o[1] = wv[i][1] * (v[i].y * inv);
+    o[2] = wv[i][2] * (v[i].z * inv);
+    o[3] = wv[i][3] * (v[i].w * inv);
     if (sizeof(TO) == 4) {
       *(float4*)((float*)yr + c) = make_float4(o[0], o[1], o[2], o[3]);
     } else {
@@ -152,6 +176,7 @@ rmsnorm_vec_kernel(float* __restrict__ x, const float* __restrict__ partial, int
       *(uint2*)((__nv_bfloat16*)yr + c) = *(uint2*)h;
     }
   }
+  MB_TRACE_END(2);
 }
 
 template <typename TW, typename TO>

@@ -128,6 +128,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                long long partial_ld, int tile_rows, int stages, int a_stage, int tiles_a,
                int tiles_b, int num_tiles, int* __restrict__ error) {
   using Cfg = TcCfg<BN>;
+  MB_TRACE_BEGIN();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
@@ -291,6 +292,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 2 * Cfg::COLS);
+  MB_TRACE_END(1);
 }
 
 // ---------------------------------------------------------------------------- CTA pairs

@@ -93,30 +93,71 @@ qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ part
                const int* __restrict__ page_table, int max_pages, int ring_pages,
                __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int nh,
                int nkv, int write_kv) {
-  mb_grid_wait();
-  mb_grid_launch_next();
+  MB_TRACE_BEGIN();
   constexpr int HD = 64 * V, HALF = 32 * V;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int head = blockIdx.y * QK_WARPS + warp;
   const int total = nh + 2 * nkv;
-  if (head >= total) return;
   const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
-  if (!is_q && !write_kv) return;
+  const bool live = head < total && (is_q || write_kv);
   const size_t col = (size_t)head * HD + V * lane;
-  float a[V], b[V];
-  if (PARTIAL) {
-#pragma unroll
-    for (int j = 0; j < V; ++j) a[j] = b[j] = 0.f;
-    const float* src0 = partial + (size_t)t * total * HD + col;
-#pragma unroll 4
-    for (int p = 0; p < parts; ++p) {
-      const float* src = src0 + (size_t)p * part_stride;
+  // Before the wait for the kernel before (which wrote the values of q, k and v, nothing
+  // else): everything that does not depend on them. The token's position and slot, the page
+  // table, the norm weights and the frequencies were settled by kernels further back, which
+  // are complete once this kernel runs (every kernel of the stream waits for the one before it
+  // ahead of letting its successor start). So the only loads after the wait are the values.
+  __nv_bfloat16* dst = nullptr;
+  float wa[V], wb[V], sn[V], cs[V];
+  bool normed = false;
+  if (live) {
+    const int pos = tok_pos[t];
+    if (is_q) {
+      dst = q_out ? q_out + (size_t)t * nh * HD + col : qkv + (size_t)t * total * HD + col;
+    } else {
+      const int g = is_k ? head - nh : head - nh - nkv;
+      const size_t row = kv_row(page_table, max_pages, ring_pages, tok_slot[t], pos, nkv, g);
+      dst = (is_k ? kpool : vpool) + row * HD + V * lane;
+    }
+    if (is_q || is_k) {
+      const void* w = is_q ? q_norm : k_norm;
+      normed = w != nullptr;
 #pragma unroll
       for (int j = 0; j < V; ++j) {
-        a[j] += __ldg(src + j);
-        b[j] += __ldg(src + HALF + j);
+        wa[j] = normed ? norm_w(w, w_bf16, V * lane + j) : 1.f;
+        wb[j] = normed ? norm_w(w, w_bf16, HALF + V * lane + j) : 1.f;
+        const float angle = inv_freq[V * lane + j] * (float)pos;  // float32 product
+        sincosf(angle, &sn[j], &cs[j]);
       }
+    }
+  }
+  mb_grid_wait();
+  mb_grid_launch_next();
+  if (!live) return;
+  float a[V], b[V];
+  if (PARTIAL) {
+    const float* src0 = partial + (size_t)t * total * HD + col;
+    // up to eight parts asked for at once, then added in split order
+#pragma unroll
+    for (int j = 0; j < V; ++j) a[j] = b[j] = 0.f;
+    for (int p0 = 0; p0 < parts; p0 += 8) {
+      float pa[8][V], pb[8][V];
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        const float* src = src0 + (size_t)(p0 + p) * part_stride;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          pa[p][j] = p0 + p < parts ? __ldg(src + j) : 0.f;
+          pb[p][j] = p0 + p < parts ? __ldg(src + HALF + j) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int p = 0; p < 8; ++p)
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          a[j] += pa[p][j];
+          b[j] += pb[p][j];
+        }
     }
   } else {
     const __nv_bfloat16* src = qkv + (size_t)t * total * HD + col;
@@ -126,18 +167,8 @@ qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ part
       b[j] = __bfloat162float(src[HALF + j]);
     }
   }
-  const int pos = tok_pos[t];
-  __nv_bfloat16* dst;
-  if (is_q) {
-    dst = q_out ? q_out + (size_t)t * nh * HD + col : qkv + (size_t)t * total * HD + col;
-  } else {
-    const int g = is_k ? head - nh : head - nh - nkv;
-    const size_t row = kv_row(page_table, max_pages, ring_pages, tok_slot[t], pos, nkv, g);
-    dst = (is_k ? kpool : vpool) + row * HD + V * lane;
-  }
   if (is_q || is_k) {
-    const void* w = is_q ? q_norm : k_norm;
-    if (w) {
+    if (normed) {
       float sum = 0.f;
 #pragma unroll
       for (int j = 0; j < V; ++j) sum = fmaf(a[j], a[j], fmaf(b[j], b[j], sum));
@@ -145,16 +176,13 @@ qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ part
       const float inv = 1.0f / sqrtf(sum / (float)HD + eps);
 #pragma unroll
       for (int j = 0; j < V; ++j) {
-        a[j] = norm_w(w, w_bf16, V * lane + j) * (a[j] * inv);
-        b[j] = norm_w(w, w_bf16, HALF + V * lane + j) * (b[j] * inv);
+        a[j] = wa[j] * (a[j] * inv);
+        b[j] = wb[j] * (b[j] * inv);
       }
     }
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-      const float angle = inv_freq[V * lane + j] * (float)pos;  // float32 product
-      float sn, cs;
-      sincosf(angle, &sn, &cs);
-      const float ra = a[j] * cs - b[j] * sn, rb = b[j] * cs + a[j] * sn;
+      const float ra = a[j] * cs[j] - b[j] * sn[j], rb = b[j] * cs[j] + a[j] * sn[j];
       a[j] = ra;
       b[j] = rb;
     }
@@ -164,6 +192,7 @@ qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ part
     dst[j] = __float2bfloat16_rn(a[j]);
     dst[HALF + j] = __float2bfloat16_rn(b[j]);
   }
+  MB_TRACE_END(3);  // by thread 0: warp 0's head is a q head, which is always live
 }
 
 // And for steps of many tokens, with 16-byte accesses: hd / 16 neighbouring lanes share a head, each holds eight neighbouring values of

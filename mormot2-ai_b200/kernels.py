@@ -112,6 +112,30 @@ class Timing:
         return out
 
 
+def read_trace() -> list:
+    """The kernels' own timeline, from a build with ``MORMOT_B200_NVCC_FLAGS=-DMB_TRACE``: every
+    CTA of the decode kernels (matrix products, RMSNorm, q/k norm + rotary, decode attention)
+    leaves its start and end on the GPU's nanosecond timer. Returns ``[(start_ns, end_ns,
+    kind)]`` of all CTAs since the last call, sorted by start (``kind``: "product", "norm",
+    "rotary", "attention"); empty in an ordinary build. Unlike ``Timing`` this does not change
+    the schedule: it shows a step as it runs inside a CUDA graph, kernels overlapping where
+    programmatic dependent launch lets them."""
+    names = {1: "product", 2: "norm", 3: "rotary", 4: "attention"}
+    rows = []
+    cap = 1 << 17
+    buf = (_c.c_ulonglong * (2 * cap))()
+    for lib in ("gemm_tc", "elementwise", "rope", "attention_mma"):
+        handle = build.load_library(lib)
+        if not hasattr(handle, "mb_trace_read"):
+            continue
+        n = handle.mb_trace_read(buf, cap)
+        mask = (1 << 56) - 1
+        rows += [(buf[2 * i] & mask, buf[2 * i + 1] & mask, names.get(buf[2 * i] >> 56, "?"))
+                 for i in range(n)]
+    rows.sort()
+    return rows
+
+
 def _call(libname: str, fn: str, argtypes, *args, launches: int = 1) -> None:
     lib = build.load_library(libname)
     f = getattr(lib, fn)
