@@ -61,7 +61,11 @@ __device__ __forceinline__ void store_out(void* C, int c_dtype, size_t idx, floa
   }
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+// silu(g) * u for an output that is rounded to bfloat16: the fast exponential and division
+// are exact to a few units of the float32 result's last place
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
 
 // Sixteen neighbouring columns b0 .. b0 + 15 of accumulator row `a` in the prefill form
 // (tokens on the lanes): store, add into the residual, leave as a partial sum, or SwiGLU.
@@ -309,11 +313,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // leaves few pairs idle.
 #define TC2_A_HALF (128 * TC_BK * 2)  // one CTA's 128 token rows of a stage
 #define TC2_COLS 256                  // tensor-memory columns of one accumulator
+#define TC2_STAGING (4 * 4096)        // 32 rows x 128 bytes of output for each epilogue warp
 template <int BN> struct Tc2Cfg {
   static constexpr int B_HALF = (BN / 2) * TC_BK * 2;  // one CTA's half of the weight rows
   static constexpr int STAGE = TC2_A_HALF + B_HALF;
   static constexpr int STAGES = (200 * 1024) / STAGE > 8 ? 8 : (200 * 1024) / STAGE;
-  static constexpr int SMEM = 1024 + STAGES * STAGE + 1024;
+  static constexpr int SMEM = 1024 + STAGES * STAGE + 1024 + TC2_STAGING;
 };
 
 template <int BN>
@@ -359,6 +364,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   cluster_sync_all();  // both CTAs' barriers and tensor memory exist before either is used
   tc_fence_after_sync();
   const uint32_t tmem = *slot_ptr;
+  // the epilogue warps' staging rows lie behind the barriers; whole 16-byte pieces of output
+  // need a width, a row stride and a base that are multiples of 16 bytes
+  const uint32_t stage_w = bars + 1024 + (warp & 3) * 4096;
+  const int out_cols = mode == TC_SWIGLU ? N >> 1 : N;
+  const int per16 = (mode == TC_SWIGLU || (mode == TC_STORE && c_dtype == MB_BF16)) ? 8 : 4;
+  const bool staged = out_cols % per16 == 0 &&
+                      (mode == TC_PARTIAL ? (partial_ld % 4 == 0 && partial_stride % 4 == 0 &&
+                                             ((uintptr_t)partial & 15) == 0)
+                                          : (ldc % per16 == 0 && ((uintptr_t)C & 15) == 0));
 
   mb_grid_wait();
   mb_grid_launch_next();
@@ -422,41 +436,92 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after_sync();
       const uint32_t taddr = tmem + b * TC2_COLS + ((uint32_t)(q * 32) << 16);
       float* part = partial ? partial + z * partial_stride : nullptr;
+      if (staged) {
+        // A thread holds one accumulator row; written from there, a warp's store would touch
+        // 32 rows with 32 bytes each. Instead the warp lays 32 rows x 128 bytes of finished
+        // output into its own shared memory (16-byte pieces, piece p of row r at
+        // p ^ (r & 7): no bank conflicts either way) and writes it out four whole rows of
+        // 128 bytes at a time.
+        const int row0 = a - lane;  // the warp's first row
+        const int acc_cols = mode == TC_SWIGLU ? 128 : (c_dtype == MB_BF16 && mode == TC_STORE ? 64 : 32);
+        const uint32_t mine = stage_w + lane * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += acc_cols) {
+          if (n0 + c0 >= N) break;
+          const int ncols = min(acc_cols, min(BN - c0, N - (n0 + c0)));
+#pragma unroll 1
+          for (int g = 0; g * 16 < ncols; ++g) {
+            float v[16];
+            tmem_ld16(taddr + c0 + 16 * g, v);
+            if (mode == TC_SWIGLU) {
+              __nv_bfloat162 h[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]),
+                                             silu_mul(v[4 * j + 2], v[4 * j + 3]));
+              st_shared_v4(mine + ((g ^ (lane & 7)) << 4), *(uint4*)&h[0]);
+            } else if (acc_cols == 64) {
+              __nv_bfloat162 h[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+              st_shared_v4(mine + (((2 * g) ^ (lane & 7)) << 4), *(uint4*)&h[0]);
+              st_shared_v4(mine + (((2 * g + 1) ^ (lane & 7)) << 4), *(uint4*)&h[4]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                st_shared_v4(mine + (((4 * g + j) ^ (lane & 7)) << 4),
+                             make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                                        __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3])));
+            }
+          }
+          __syncwarp();
+          const int pc = lane & 7;
+          // bytes of output per accumulator column: 1 (SwiGLU), 2 (bfloat16), 4 (float32)
+          const int pieces = mode == TC_SWIGLU ? ncols >> 4 : (acc_cols == 64 ? ncols >> 3 : ncols >> 2);
+          if (acc_cols == 32) {
+            float* dst = mode == TC_PARTIAL ? part : (float*)C;
+            const long long ld = mode == TC_PARTIAL ? partial_ld : ldc;
+            float4 old[8];
+            if (mode == TC_ADD) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int r = 4 * i + (lane >> 3);
+                if (pc < pieces && row0 + r < M)
+                  old[i] = *(const float4*)(dst + (size_t)(row0 + r) * ld + n0 + c0 + 4 * pc);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = 4 * i + (lane >> 3);
+              if (pc < pieces && row0 + r < M) {
+                const uint4 u = ld_shared_v4(stage_w + r * 128 + ((pc ^ (r & 7)) << 4));
+                float4 o = make_float4(__uint_as_float(u.x), __uint_as_float(u.y),
+                                       __uint_as_float(u.z), __uint_as_float(u.w));
+                if (mode == TC_ADD) { o.x += old[i].x; o.y += old[i].y; o.z += old[i].z; o.w += old[i].w; }
+                *(float4*)(dst + (size_t)(row0 + r) * ld + n0 + c0 + 4 * pc) = o;
+              }
+            }
+          } else {
+            const int col = (mode == TC_SWIGLU ? (n0 + c0) >> 1 : n0 + c0) + 8 * pc;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = 4 * i + (lane >> 3);
+              if (pc < pieces && row0 + r < M)
+                *(uint4*)((__nv_bfloat16*)C + (size_t)(row0 + r) * ldc + col) =
+                    ld_shared_v4(stage_w + r * 128 + ((pc ^ (r & 7)) << 4));
+            }
+          }
+          __syncwarp();  // the rows are read out before the next columns are laid over them
+        }
+      } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         if (n0 + c0 >= N) break;
         float v[16];
         tmem_ld16(taddr + c0, v);
-        // adding into the float32 residual: a whole 128-byte line of the row (32 columns) is
-        // asked for together, and the next line is brought near while this one is added. The
-        // condition is the same for the whole warp (the loads from tensor memory are
-        // warp-wide instructions); only the memory accesses depend on the thread's row.
-        if (mode == TC_ADD && c_dtype == MB_F32 && c0 + 32 <= BN && n0 + c0 + 32 <= N &&
-            (ldc & 3) == 0 && ((uintptr_t)C & 15) == 0) {
-          float v2[16];
-          tmem_ld16(taddr + c0 + 16, v2);
-          if (a < M) {
-            float4* p = (float4*)((float*)C + (size_t)a * ldc + n0 + c0);
-            if (c0 + 64 <= BN && n0 + c0 + 64 <= N)
-              asm volatile("prefetch.global.L2 [%0];" ::"l"(p + 8));
-            float4 r[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) r[j] = p[j];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              r[j].x += v[4 * j]; r[j].y += v[4 * j + 1];
-              r[j].z += v[4 * j + 2]; r[j].w += v[4 * j + 3];
-              r[4 + j].x += v2[4 * j]; r[4 + j].y += v2[4 * j + 1];
-              r[4 + j].z += v2[4 * j + 2]; r[4 + j].w += v2[4 * j + 3];
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) p[j] = r[j];
-          }
-          c0 += 16;  // two steps of columns done
-          continue;
-        }
         if (a < M)
           store_row16(v, C, c_dtype, ldc, a, n0 + c0, N, mode, part, partial_ld, partial_stride);
+      }
       }
       tc_fence_before_sync();
       __syncwarp();
