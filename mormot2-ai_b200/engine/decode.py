@@ -38,8 +38,11 @@ class DecodeRun:
     DEPTH = 4
 
     def __init__(self, engine, ctx, slots: List[int], tokens: List[int], max_steps: int,
-                 sampler, sampling, vocab_limit: Optional[int], history: bool):
+                 sampler, sampling, vocab_limit: Optional[int], history: bool,
+                 order: Optional[List[int]] = None):
+        # ``order[j]``: which of ``slots`` row j of ``ctx`` (and of every step's picks) is
         self.engine, self.ctx, self.slots = engine, ctx, slots
+        self.order = None if order is None or order == sorted(order) else list(order)
         self.first_tokens = tokens
         self.max_steps = max_steps
         self.sampler, self.sampling, self.vocab_limit = sampler, sampling, vocab_limit
@@ -79,10 +82,27 @@ class DecodeRun:
         if self.n_read >= self.launched:
             raise InferError("no launched step is unread")
         got = self.engine.rt.take_mail(self.n_read % self.DEPTH, self.ctx.B)
+        if self.order is not None:
+            rows, got = got, [0] * len(got)
+            for j, i in enumerate(self.order):
+                got[i] = rows[j]
         self.d2h_bytes += 4 * (1 + self.ctx.B)
         self.n_read += 1
         self.picks.append(got)
         return got
+
+    def picks_on_device(self) -> torch.Tensor:
+        """The picks of a run opened with ``history``: ``[steps, sequences]`` in the order of
+        the run's slots (int32, on the device)."""
+        if self.history is None:
+            raise InferError("the run was not opened with history")
+        if self.order is None:
+            return self.history
+        back = [0] * len(self.order)
+        for j, i in enumerate(self.order):
+            back[i] = j
+        return self.history.index_select(
+            1, torch.tensor(back, dtype=torch.int64, device=self.history.device))
 
     # ------------------------------------------------------------------ ending
     def finish(self, kept: Optional[Sequence[int]] = None) -> None:

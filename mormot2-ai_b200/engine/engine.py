@@ -396,11 +396,15 @@ class Engine:
             seqs.append((slot, past, [int(t)], [0]))
         self.cache.map_pages(self.book.reserve(
             [(s, p + n) for (s, p, _, _), n in zip(seqs, steps)]))
-        ctx = self.buffers.fill(seqs)
+        # Inside the run the longest sequence comes first: the attention's CTAs start in the
+        # order of the rows, and the long ones must not be the last to start. The order holds
+        # for the whole run, since every sequence grows by one position a step.
+        order = sorted(range(len(seqs)), key=lambda i: -seqs[i][1])
+        ctx = self.buffers.fill([seqs[i] for i in order])
         self.last_h2d_bytes = 4 * (4 * ctx.T + 3 * ctx.B + 1 + ctx.n_want)
         self.last_slots, self.last_passes = ctx.seq_slot, 1
         self.run = DecodeRun(self, ctx, list(slots), [int(t) for t in tokens], min(steps),
-                             sampler, sampling, vocab_limit, history)
+                             sampler, sampling, vocab_limit, history, order)
         return self.run
 
     def decode_steps(self, slots: Sequence[int], tokens: Sequence[int], n_steps: int, sampler,
@@ -419,7 +423,7 @@ class Engine:
             run.abandon()
             raise
         run.finish()
-        return run.history[:n_steps]
+        return run.picks_on_device()[:n_steps]
 
     def _passes(self, plan):
         """Cuts a step into passes of at most ``prefill_chunk`` new tokens per sequence and
