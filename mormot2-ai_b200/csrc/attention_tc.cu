@@ -372,19 +372,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
     mbar_wait(o_done0 + 8 * ((n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1, error, 18);
     tc_fence_after_sync();
     const float inv = 1.0f / l;
-    const bool mine = row0 + row < n_new;
-    bf16* dst = out + (size_t)(start + row0 + row) * out_stride + (size_t)h * AT_HD;
+    // A thread holds one row of O; written from there, a warp's store would touch 32 rows with
+    // 16 bytes each. Q's shared memory is free now (every product is done): the warp lays its
+    // 32 rows of 256 bytes there (16-byte piece p of row r at p ^ (r & 7): no bank conflicts
+    // either way) and writes them out two whole rows at a time.
+    const uint32_t stage = sQ + (uint32_t)q * (32 * AT_HD * 2);
 #pragma unroll 1
     for (int c0 = 0; c0 < AT_HD; c0 += 16) {
       float o[16];
       tmem_ld16(tO + lane_addr + c0, o);
-      if (mine) {
-        __nv_bfloat162 hv[8];
+      uint32_t w[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) hv[i] = __floats2bfloat162_rn(o[2 * i] * inv, o[2 * i + 1] * inv);
-        uint4* p = (uint4*)(dst + c0);
-        p[0] = *(uint4*)&hv[0];
-        p[1] = *(uint4*)&hv[4];
+      for (int i = 0; i < 8; ++i) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(o[2 * i] * inv, o[2 * i + 1] * inv);
+        w[i] = *reinterpret_cast<uint32_t*>(&v);
+      }
+      const int pc = c0 >> 3;
+      st_shared_v4(stage + lane * (AT_HD * 2) + ((pc ^ (lane & 7)) << 4),
+                   make_uint4(w[0], w[1], w[2], w[3]));
+      st_shared_v4(stage + lane * (AT_HD * 2) + (((pc + 1) ^ (lane & 7)) << 4),
+                   make_uint4(w[4], w[5], w[6], w[7]));
+    }
+    __syncwarp();
+    const int pc = lane & 15;
+#pragma unroll 4
+    for (int i = 0; i < 16; ++i) {
+      const int r = 2 * i + (lane >> 4);
+      if (row0 + q * 32 + r < n_new) {
+        const uint4 v = ld_shared_v4(stage + r * (AT_HD * 2) + ((pc ^ (r & 7)) << 4));
+        *(uint4*)(out + (size_t)(start + row0 + q * 32 + r) * out_stride + (size_t)h * AT_HD +
+                  8 * pc) = v;
       }
     }
   }
