@@ -126,10 +126,11 @@ __device__ __forceinline__ unsigned long long mb_now() {
 #define MB_TRACE_END(id_)                                                         \
   do {                                                                            \
     if (threadIdx.x == 0) {                                                       \
+      const unsigned long long t1_ = mb_now(); /* before the atomic's round trip */ \
       const unsigned int i_ = atomicAdd(&g_mb_trace_n, 1u);                       \
       if (i_ < MB_TRACE_CAP) {                                                    \
         g_mb_trace[i_][0] = (mb_t0_ & 0x00ffffffffffffffull) | ((unsigned long long)(id_) << 56); \
-        g_mb_trace[i_][1] = mb_now();                                             \
+        g_mb_trace[i_][1] = t1_;                                                  \
       }                                                                           \
     }                                                                             \
   } while (0)
