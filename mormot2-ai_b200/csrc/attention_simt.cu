@@ -1,8 +1,10 @@
 // Causal grouped-query attention over the paged cache for any head size up to 256 and any
 // number of heads and groups, in float32 arithmetic on the CUDA cores, for float32 or
 // bfloat16 storage. One warp per (token, query head) walks the keys of the token's own
-// sequence in tiles of 32 with an online softmax. It serves prefill and decode of the true
-// 32-bit path and is the fallback of the bfloat16 path.
+// sequence in tiles of 32 with an online softmax (a lane has one key of the tile for q·k and
+// four neighbouring values of every key's row for p·v; 16-byte loads where the head size and
+// the strides are multiples of four, single values else). It serves prefill and decode of the
+// true 32-bit path and is the fallback of the bfloat16 path.
 //
 // The formula is the reference's (paths within the reference project):
 // src/infer/mormot.ai.infer.backend.cpu.pas:1296-1353 — head h reads KV head
@@ -15,7 +17,7 @@ MB_DEFINE_LAST_ERROR
 #define ATT_WARPS 4
 #define ATT_MAX_D 8  // head sizes up to 32 * 8
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                       const T* __restrict__ kpool, const T* __restrict__ vpool,
@@ -23,7 +25,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
                       const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                       const int* __restrict__ seq_slot, int nh, int nkv, int hd, int window,
                       float scale) {
-  extern __shared__ float qs[];  // ATT_WARPS x hd
+  extern __shared__ __align__(16) float qs[];  // ATT_WARPS x hd
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int h = blockIdx.y * ATT_WARPS + warp;
@@ -39,6 +41,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
   int lo = 0;
   if (window > 0 && pos + 1 > window) lo = pos + 1 - window;
   float m = -INFINITY, l = 0.f;
+  // VEC: values 4 * lane .. + 3 of every 128; else values lane, lane + 32, ...
   float acc[ATT_MAX_D];
 #pragma unroll
   for (int d = 0; d < ATT_MAX_D; ++d) acc[d] = 0.f;
@@ -52,7 +55,14 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
       row = kv_row(page_table, max_pages, ring_pages, slot, kp, nkv, g);
       const T* kr = kpool + row * hd;
       float dot = 0.f;
-      for (int i = 0; i < hd; ++i) dot = fmaf(qv[i], to_f32<T>(kr[i]), dot);
+      if (VEC) {
+        for (int i = 0; i < hd; i += 4) {
+          const float4 kk = load4<T>(kr + i), qq = *(const float4*)(qv + i);
+          dot = fmaf(qq.x, kk.x, fmaf(qq.y, kk.y, fmaf(qq.z, kk.z, fmaf(qq.w, kk.w, dot))));
+        }
+      } else {
+        for (int i = 0; i < hd; ++i) dot = fmaf(qv[i], to_f32<T>(kr[i]), dot);
+      }
       s = dot * scale;
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -68,19 +78,43 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
       const unsigned lo32 = __shfl_sync(0xffffffffu, (unsigned)(row & 0xffffffffu), j);
       const unsigned hi32 = __shfl_sync(0xffffffffu, (unsigned)(row >> 32), j);
       const T* vr = vpool + (((size_t)hi32 << 32) | lo32) * hd;
+      if (VEC) {
 #pragma unroll
-      for (int d = 0; d < ATT_MAX_D; ++d) {
-        const int i = lane + 32 * d;
-        if (i < hd) acc[d] = fmaf(pj, to_f32<T>(vr[i]), acc[d]);
+        for (int d = 0; d < ATT_MAX_D / 4; ++d) {
+          const int i = 4 * lane + 128 * d;
+          if (i < hd) {
+            const float4 vv = load4<T>(vr + i);
+            acc[4 * d] = fmaf(pj, vv.x, acc[4 * d]);
+            acc[4 * d + 1] = fmaf(pj, vv.y, acc[4 * d + 1]);
+            acc[4 * d + 2] = fmaf(pj, vv.z, acc[4 * d + 2]);
+            acc[4 * d + 3] = fmaf(pj, vv.w, acc[4 * d + 3]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int d = 0; d < ATT_MAX_D; ++d) {
+          const int i = lane + 32 * d;
+          if (i < hd) acc[d] = fmaf(pj, to_f32<T>(vr[i]), acc[d]);
+        }
       }
     }
   }
   const float inv = 1.0f / l;
   T* op = out + (size_t)t * out_stride + (size_t)h * hd;
+  if (VEC) {
 #pragma unroll
-  for (int d = 0; d < ATT_MAX_D; ++d) {
-    const int i = lane + 32 * d;
-    if (i < hd) op[i] = from_f32<T>(acc[d] * inv);
+    for (int d = 0; d < ATT_MAX_D / 4; ++d) {
+      const int i = 4 * lane + 128 * d;
+      if (i < hd)
+        store4<T>(op + i, make_float4(acc[4 * d] * inv, acc[4 * d + 1] * inv, acc[4 * d + 2] * inv,
+                                      acc[4 * d + 3] * inv));
+    }
+  } else {
+#pragma unroll
+    for (int d = 0; d < ATT_MAX_D; ++d) {
+      const int i = lane + 32 * d;
+      if (i < hd) op[i] = from_f32<T>(acc[d] * inv);
+    }
   }
 }
 
@@ -100,15 +134,19 @@ MB_EXPORT int mb_attention_simt(const void* q, int q_stride, void* out, int out_
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(T, (nh + ATT_WARPS - 1) / ATT_WARPS);
   const size_t smem = (size_t)ATT_WARPS * hd * sizeof(float);
-  if (dtype == MB_F32)
-    attention_simt_kernel<float><<<grid, ATT_WARPS * 32, smem, s>>>(
-        (const float*)q, q_stride, (float*)out, out_stride, (const float*)kpool,
-        (const float*)vpool, page_table, max_pages, ring_pages, tok_seq, tok_pos, seq_slot, nh,
-        nkv, hd, window, scale);
-  else
-    attention_simt_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, smem, s>>>(
-        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
-        (const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, max_pages,
-        ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, hd, window, scale);
+  // four values with one load: the size of four values divides every row's address
+  const int four = dtype == MB_F32 ? 15 : 7;
+  const bool vec = hd % 4 == 0 && q_stride % 4 == 0 && out_stride % 4 == 0 &&
+                   (((uintptr_t)q | (uintptr_t)out | (uintptr_t)kpool | (uintptr_t)vpool) & four) == 0;
+#define GO(T_, V_)                                                                            \
+  attention_simt_kernel<T_, V_><<<grid, ATT_WARPS * 32, smem, s>>>(                           \
+      (const T_*)q, q_stride, (T_*)out, out_stride, (const T_*)kpool, (const T_*)vpool,       \
+      page_table, max_pages, ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, hd, window, scale)
+  if (dtype == MB_F32) {
+    if (vec) GO(float, true); else GO(float, false);
+  } else {
+    if (vec) GO(__nv_bfloat16, true); else GO(__nv_bfloat16, false);
+  }
+#undef GO
   MB_CHECK_LAUNCH("mb_attention_simt");
 }

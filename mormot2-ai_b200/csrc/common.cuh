@@ -168,6 +168,27 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
   return __float2bfloat16_rn(v);
 }
 
+// Four consecutive values as float32 (p aligned to the four values' size) and back
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) {
+  return *(const float4*)p;
+}
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *(const uint2*)p;
+  const float2 lo = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x);
+  const float2 hi = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *(float4*)p = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *(const unsigned int*)&lo;
+  raw.y = *(const unsigned int*)&hi;
+  *(uint2*)p = raw;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

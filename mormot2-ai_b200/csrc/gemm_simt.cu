@@ -93,9 +93,97 @@ gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, TC
   }
 }
 
+// ---------------------------------------------------------------------------- few rows
+// The same product for at most 16 rows of A (a decode step): the weight streams through once.
+// A warp owns four weight rows (four output features, or two with their gate and up rows) and
+// walks K in chunks of 128 (every lane 4 consecutive values of each of its rows, 16 bytes of
+// float32), against up to eight rows of A at a time; 32 sums a warp, reduced by shuffles.
+#define FEW_ROWS 8   // rows of A in one pass
+#define FEW_MAX 16   // the most rows that take this kernel
+
+template <typename TA, typename TW, typename TC, int EPI>
+__global__ void __launch_bounds__(256)
+gemm_few_rows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W,
+                     TC* __restrict__ C, int ldc, int M, int N, int K) {
+  constexpr bool GLU = EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_PAIRS;
+  constexpr int FEATS = GLU ? 2 : 4;  // output features of a warp
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * 8 + warp) * FEATS;
+  if (n0 >= N) return;
+  // the warp's four weight rows; a row beyond the weight is read as row n0's and not stored
+  const TW* wr[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    int row;
+    if (EPI == EPI_SWIGLU) row = (j >> 1) * N + min(n0 + (j & 1), N - 1);     // g0 g1 u0 u1
+    else if (EPI == EPI_SWIGLU_PAIRS) row = 2 * min(n0 + (j >> 1), N - 1) + (j & 1);  // g0 u0 g1 u1
+    else row = min(n0 + j, N - 1);
+    wr[j] = W + (size_t)row * K;
+  }
+  for (int m0 = 0; m0 < M; m0 += FEW_ROWS) {
+    float acc[4][FEW_ROWS];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int m = 0; m < FEW_ROWS; ++m) acc[j][m] = 0.f;
+    for (int k = lane * 4; k < K; k += 128) {
+      float4 w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = load4<TW>(wr[j] + k);
+#pragma unroll
+      for (int m = 0; m < FEW_ROWS; ++m) {
+        if (m0 + m >= M) break;  // uniform over the warp
+        const float4 a = load4<TA>(A + (size_t)(m0 + m) * lda + k);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          acc[j][m] = fmaf(a.x, w[j].x, fmaf(a.y, w[j].y, fmaf(a.z, w[j].z, fmaf(a.w, w[j].w, acc[j][m]))));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int m = 0; m < FEW_ROWS; ++m) acc[j][m] = warp_sum(acc[j][m]);
+    // lane m stores row m0 + m
+#pragma unroll
+    for (int m = 0; m < FEW_ROWS; ++m) {
+      if (lane != m || m0 + m >= M) continue;
+#pragma unroll
+      for (int f = 0; f < FEATS; ++f) {
+        if (n0 + f >= N) continue;
+        TC* out = C + (size_t)(m0 + m) * ldc + n0 + f;
+        if (EPI == EPI_STORE) {
+          *out = from_f32<TC>(acc[f][m]);
+        } else if (EPI == EPI_ADD) {
+          *out = from_f32<TC>(to_f32<TC>(*out) + acc[f][m]);
+        } else {
+          const float g = EPI == EPI_SWIGLU ? acc[f][m] : acc[2 * f][m];
+          const float u = EPI == EPI_SWIGLU ? acc[2 + f][m] : acc[2 * f + 1][m];
+          *out = from_f32<TC>(g / (1.0f + expf(-g)) * u);
+        }
+      }
+    }
+  }
+}
+
 template <typename TA, typename TW, typename TC>
 static int launch(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K,
                   int epi, cudaStream_t s) {
+  // few rows, and every row piece of 4 values a whole aligned load
+  const int a_align = sizeof(TA) == 4 ? 15 : 7, w_align = sizeof(TW) == 4 ? 15 : 7;
+  if (M <= FEW_MAX && K % 4 == 0 && lda % 4 == 0 && ((uintptr_t)A & a_align) == 0 &&
+      ((uintptr_t)W & w_align) == 0) {
+    const int feats = (epi == EPI_SWIGLU || epi == EPI_SWIGLU_PAIRS) ? 2 : 4;
+    const int blocks = (N + 8 * feats - 1) / (8 * feats);
+#define FEW(E)                                                                                \
+  gemm_few_rows_kernel<TA, TW, TC, E><<<blocks, 256, 0, s>>>((const TA*)A, lda, (const TW*)W, \
+                                                             (TC*)C, ldc, M, N, K)
+    if (epi == EPI_STORE) FEW(EPI_STORE);
+    else if (epi == EPI_ADD) FEW(EPI_ADD);
+    else if (epi == EPI_SWIGLU) FEW(EPI_SWIGLU);
+    else FEW(EPI_SWIGLU_PAIRS);
+#undef FEW
+    MB_CHECK_LAUNCH("mb_gemm_simt");
+  }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) MB_FAIL("mb_gemm_simt: %d rows are too many for one launch", M);
 #define GO(E)                                                                                  \
