@@ -98,6 +98,25 @@ gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, TC
 // A warp owns four weight rows (four output features, or two with their gate and up rows) and
 // walks K in chunks of 128 (every lane 4 consecutive values of each of its rows, 16 bytes of
 // float32), against up to eight rows of A at a time; 32 sums a warp, reduced by shuffles.
+// a weight row's values are used once: they pass by the L1 cache, which keeps the rows of A
+template <typename T> __device__ __forceinline__ float4 load4_once(const T* p);
+template <> __device__ __forceinline__ float4 load4_once<float>(const float* p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+template <> __device__ __forceinline__ float4 load4_once<__nv_bfloat16>(const __nv_bfloat16* p) {
+  uint2 raw;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0, %1}, [%2];"
+               : "=r"(raw.x), "=r"(raw.y)
+               : "l"(p));
+  const float2 lo = __bfloat1622float2(*(const __nv_bfloat162*)&raw.x);
+  const float2 hi = __bfloat1622float2(*(const __nv_bfloat162*)&raw.y);
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
 #define FEW_ROWS 8   // rows of A in one pass
 #define FEW_MAX 16   // the most rows that take this kernel
 
@@ -129,7 +148,7 @@ gemm_few_rows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W
     for (int k = lane * 4; k < K; k += 128) {
       float4 w[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) w[j] = load4<TW>(wr[j] + k);
+      for (int j = 0; j < 4; ++j) w[j] = load4_once<TW>(wr[j] + k);
 #pragma unroll
       for (int m = 0; m < FEW_ROWS; ++m) {
         if (m0 + m >= M) break;  // uniform over the warp

@@ -101,7 +101,8 @@ def test_swiglu(dtype):
     assert rel(out.float().cpu(), want) <= (2e-6 if dtype == "float32" else 8e-3)
 
 
-@pytest.mark.parametrize("M,N,Kd", [(1, 7, 5), (3, 509, 96), (70, 65, 33), (130, 200, 320)])
+@pytest.mark.parametrize("M,N,Kd", [(1, 7, 5), (3, 509, 96), (70, 65, 33), (130, 200, 320),
+                                    (12, 131, 200), (16, 64, 1028), (17, 37, 132)])
 @pytest.mark.parametrize("a_dt,w_dt,c_dt", [("float32", "float32", "float32"),
                                             ("bfloat16", "bfloat16", "bfloat16"),
                                             ("bfloat16", "float32", "float32"),
