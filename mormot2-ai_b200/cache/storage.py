@@ -11,6 +11,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
+import numpy as np
 import torch
 
 from .guards import Guards, alloc
@@ -76,10 +77,9 @@ class CacheStorage:
             if not entries:
                 continue
             host = self.tables_host[g]
-            lo, hi = host.shape[0], -1
-            for slot, entry, page in entries:
-                host[slot, entry] = page
-                lo, hi = min(lo, slot), max(hi, slot)
+            where = np.asarray(entries, dtype=np.int64)     # [n, 3]: slot, entry, page
+            host.numpy()[where[:, 0], where[:, 1]] = where[:, 2]
+            lo, hi = int(where[:, 0].min()), int(where[:, 0].max())
             self.tables[g][lo:hi + 1].copy_(host[lo:hi + 1])
 
     def table_faults(self, book: CacheBook) -> List[str]:

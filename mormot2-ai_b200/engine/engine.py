@@ -304,7 +304,7 @@ class Engine:
             raise
         for slot, past, tokens, _ in plan:
             self.book.commit(slot, past + len(tokens))
-            self.ids[slot].extend(int(t) for t in tokens)
+            self.ids[slot].extend(tokens.tolist() if isinstance(tokens, np.ndarray) else tokens)
         return out
 
     def timed_step(self, entries: Sequence[Entry]):
