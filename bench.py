@@ -284,8 +284,9 @@ def clocked(fn, *args, **kw):
 
 def other_shapes(torch, a, pts):
     """The Qwen3-0.6B shape with 64 prompts of unequal lengths (one prefill step, then 256
-    decode steps) and the Qwen3-32B shape (prefill of 2,048 tokens, decode at batch 1 and 8
-    toward a context of 4,096). Each engine is made, measured and dropped."""
+    decode steps), the 8B shape decoding at a context of 32,768 (batch 1 and 8), and the
+    Qwen3-32B shape (prefill of 2,048 tokens, decode at batch 1 and 8 toward a context of
+    4,096). Each engine is made, measured and dropped."""
     from mormot2_ai_b200 import Engine
     from mormot2_ai_b200.sampling import DeviceSampler, Sampling
     greedy = Sampling()
@@ -302,6 +303,21 @@ def other_shapes(torch, a, pts):
     (ms, held, _), rec = clocked(timed_decode, torch, eng, sampler, greedy, lens, steps, warm, 30)
     pts.decode("ragged_0p6b_decode", cfg, ms, steps, 64, held, rec)
     pts.detail["ragged_0p6b_decode"]["prompt_lens"] = f"uniform 16..2048, seed 3, sum {sum(lens)}"
+    del eng, sampler
+    torch.cuda.empty_cache()
+    # -- the 8B shape at a context of 32,768: the cache, not the weights, is most of a step
+    cfg = model_config(36)
+    long_context = 32768
+    eng = Engine.from_random(cfg, seed=2, std=0.02, max_tokens=8 * long_context,
+                             max_context=long_context, max_slots=8, prefill_chunk=4096,
+                             max_step_tokens=8192)
+    sampler = DeviceSampler(eng.rt.device, eng.max_slots, eng.vocab_size)
+    steps = min(a.steps, 32)
+    for b in (1, 8):
+        lens = [long_context - steps - warm - SETTLE] * b
+        (ms, held, _), rec = clocked(timed_decode, torch, eng, sampler, greedy, lens, steps, warm,
+                                     50 + b)
+        pts.decode(f"decode_b{b}_ctx{long_context}", cfg, ms, steps, b, held, rec)
     del eng, sampler
     torch.cuda.empty_cache()
     # -- 32B

@@ -16,6 +16,12 @@ import torch
 from ..errors import InferError
 
 
+# A pass whose longest sequence has at least this many positions may be planned differently by
+# the kernels (a decode attention that deals a long sequence out over more CTAs): the engine
+# keeps a captured graph of its own for such passes.
+LONG_CONTEXT = 24576
+
+
 @dataclass
 class StepContext:
     T: int                      # tokens in this pass
@@ -36,6 +42,10 @@ class StepContext:
     host_new: List[int]
     host_past: List[int]
     host_slots: List[int]
+
+    @property
+    def long(self) -> bool:
+        return self.max_len >= LONG_CONTEXT
 
 
 class StepBuffers:

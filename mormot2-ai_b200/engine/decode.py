@@ -65,6 +65,7 @@ class DecodeRun:
         if self.history is None and self.launched - self.n_read >= self.DEPTH:
             raise InferError(f"{self.DEPTH} launched steps are unread: read one first")
         eng, ctx, rt = self.engine, self.ctx, self.engine.rt
+        ctx.max_len = max(self.past) + self.launched + 1   # the positions moved on on the device
         logits = eng._forward(ctx)
         self.sampler.pick(logits, ctx.seq_slot, self.sampling, self.vocab_limit, out=self.box)
         K.advance_decode(ctx.tok_ids, ctx.tok_pos, self.box,

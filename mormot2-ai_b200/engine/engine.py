@@ -334,7 +334,7 @@ class Engine:
         and are overwritten by the next replay of the same shape."""
         if not (self.use_graphs and ctx.decode and self.on_state is None):
             return self.model.forward(ctx, self.cache, self.on_state)
-        key = (ctx.B, ctx.n_want)
+        key = (ctx.B, ctx.n_want, ctx.long)
         g = self.graphs.get(key)
         if g is None:
             out = self.model.forward(ctx, self.cache)     # this step's result, computed eagerly

@@ -43,6 +43,10 @@ class Runtime:
                                     self.device, None) for i in range(2)]
                              if self.fast_kernels else None)
         self.pending_turn = 0
+        # partial results of a decode attention whose splits are too many for one cluster
+        self.attention_scratch = (alloc(guards, "attention split results", (1 << 20,),
+                                        torch.float32, self.device, None)
+                                  if self.fast_kernels else None)
         # word 0: set by a kernel when one of its bounded waits ran out; the words after it: the
         # tokens that the sampler chose in a step, so that one copy brings both to the host
         self.mailbox = alloc(guards, "mailbox", (1 + MAILBOX_TOKENS,), torch.int32, self.device)

@@ -165,6 +165,48 @@ def test_a_sequence_keeps_fewer_steps_than_were_launched(tiny_a_model):
         eng.decode_run([slots[0], slots[0]], [1, 1], [2, 2], sampler, greedy)
 
 
+@pytest.mark.parametrize("batch", [1, 2])
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_a_long_sequence_is_dealt_out_over_more_ctas(name, batch, tmp_path_factory, monkeypatch):
+    """One or two sequences that grow past the length from which the decode attention deals a
+    sequence out over about one CTA per SM (through scratch memory and a second kernel, in the
+    layer without a window): the run changes to the graph of its own in mid-run, and every
+    pick stays the plain implementation's. The length is lowered to what a tiny model holds."""
+    from mormot2_ai_b200 import kernels as K
+    from mormot2_ai_b200.engine import batch as batch_module
+    from tests.conftest import TinyModel
+    tiny = TinyModel(name, str(tmp_path_factory.mktemp("long_" + name)))
+    monkeypatch.setattr(batch_module, "LONG_CONTEXT", 150)
+    calls = []
+    plain_entry = K.attention_decode
+    monkeypatch.setattr(K, "attention_decode",
+                        lambda *a, **k: (calls.append(a[10]), plain_entry(*a, **k))[1])
+    eng = Engine.from_folder(tiny.folder, dtype="bfloat16", max_tokens=1024, max_slots=2)
+    sampler = DeviceSampler(eng.rt.device, eng.max_slots, eng.vocab_size)
+    greedy = Sampling()
+    prompts = [tiny.tokens(n, seed=70 + n) for n in (131, 90)[:batch]]
+    slots = [eng.open() for _ in prompts]
+    logits = eng.step([Entry(s, p) for s, p in zip(slots, prompts)])
+    firsts = sampler.pick(logits, eng.last_slots, greedy).tolist()
+    steps = 60
+    run = eng.decode_run(slots, firsts, [steps] * batch, sampler, greedy)
+    rows = []
+    for _ in range(steps):
+        run.launch()
+        rows.append(run.read())
+    run.finish()
+    eng.rt.check()
+    assert (batch, batch, False) in eng.graphs and (batch, batch, True) in eng.graphs
+    assert calls and min(calls) > 8, calls          # more splits than a cluster holds
+    for b, p in enumerate(prompts):
+        check_picks(tiny, "bfloat16", p, [firsts[b]] + [r[b] for r in rows], 0.0, 0)
+    # and an ordinary step of a long sequence: the logits are the plain ones
+    ids = list(prompts[0]) + [firsts[0]] + [r[0] for r in rows]
+    out = eng.step([Entry(slots[0], [ids[-1]])]).cpu().numpy()
+    ok, err = close(out, tiny.reference(ids)[-1:], "bfloat16")
+    assert ok, err
+
+
 def test_batch_64_at_the_sizes_of_a_real_model():
     """Two layers with the sizes of a real model, 64 sequences of unequal lengths between 20
     and 700 tokens, decoded on the device: the decode products at 64 tokens, the cluster
