@@ -260,7 +260,9 @@ def test_attention_over_the_paged_cache(kind, nh, nkv, hd, dtype):
         q = torch.tensor(rng.standard_normal((T, nh * hd)), dtype=torch.float32).to(dt)
         out = torch.empty(T, nh * hd, dtype=dt, device=DEV)
         scale = 1.0 / math.sqrt(hd)
-        for splits in ((1, 3, 4, 7, 8) if kind.startswith("decode") else (None,)):
+        # more splits than a sequence has pages, and more than a cluster holds (scratch form)
+        many = (18, 32) if kind == "decode" else ()
+        for splits in ((1, 3, 4, 7, 8) + many if kind.startswith("decode") else (None,)):
             out.zero_()
             run_attention(kind, q.to(DEV), out, step, line, nh, nkv, hd, window, scale, splits)
             got = out.float().cpu().numpy().reshape(T, nh, hd)
