@@ -184,6 +184,113 @@ gemm_few_rows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W
   }
 }
 
+// ---------------------------------------------------------------------------- many rows
+// The same product for many rows: 128 x 128 tiles, 8 x 8 results a thread (two 4 x 4 quarters
+// 64 apart in each direction, so that the shared-memory reads are 16 bytes wide and free of
+// bank conflicts), K in steps of 16 through two buffers with the next step's global loads under
+// way while this one is multiplied. Epilogues: store, residual add, and SwiGLU over weight rows
+// that alternate gate and up (NW = 2 N weight rows, neighbouring columns of the tile pair up).
+#define LM 128
+#define LN 128
+#define LK 16
+
+// four values k .. k + 3 of a row as float32, zeros beyond K or for a row that does not exist
+template <typename T>
+__device__ __forceinline__ float4 row_piece(const T* __restrict__ base, bool row_ok, int k, int K,
+                                            bool vec) {
+  if (!row_ok || k >= K) return make_float4(0.f, 0.f, 0.f, 0.f);
+  if (vec) return load4<T>(base + k);
+  float4 v;
+  v.x = to_f32<T>(base[k]);
+  v.y = k + 1 < K ? to_f32<T>(base[k + 1]) : 0.f;
+  v.z = k + 2 < K ? to_f32<T>(base[k + 2]) : 0.f;
+  v.w = k + 3 < K ? to_f32<T>(base[k + 3]) : 0.f;
+  return v;
+}
+
+template <typename TA, typename TW, typename TC, int EPI>
+__global__ void __launch_bounds__(256)
+gemm_many_rows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W,
+                      TC* __restrict__ C, int ldc, int M, int NW, int K, int vec_a, int vec_w) {
+  __shared__ __align__(16) float As[2][LK][LM + 4];
+  __shared__ __align__(16) float Ws[2][LK][LN + 4];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * LM, n0 = blockIdx.x * LN;
+  // loads: thread t brings values 8 (t % 2) .. + 7 of row t / 2 of both tiles
+  const int lr = tid >> 1, lk = (tid & 1) * 8;
+  const bool a_ok = m0 + lr < M, w_ok = n0 + lr < NW;
+  const TA* arow = A + (size_t)(m0 + lr) * lda;
+  const TW* wrow = W + (size_t)(n0 + lr) * K;
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+  float4 ra[2], rw[2];
+  auto fetch = [&](int k) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      ra[h] = row_piece<TA>(arow, a_ok, k + lk + 4 * h, K, vec_a);
+      rw[h] = row_piece<TW>(wrow, w_ok, k + lk + 4 * h, K, vec_w);
+    }
+  };
+  auto put = [&](int buf) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int k = lk + 4 * h;
+      As[buf][k][lr] = ra[h].x; As[buf][k + 1][lr] = ra[h].y;
+      As[buf][k + 2][lr] = ra[h].z; As[buf][k + 3][lr] = ra[h].w;
+      Ws[buf][k][lr] = rw[h].x; Ws[buf][k + 1][lr] = rw[h].y;
+      Ws[buf][k + 2][lr] = rw[h].z; Ws[buf][k + 3][lr] = rw[h].w;
+    }
+  };
+  int cur = 0;
+  fetch(0);
+  put(0);
+  __syncthreads();
+  for (int k0 = 0; k0 < K; k0 += LK) {
+    const bool more = k0 + LK < K;
+    if (more) fetch(k0 + LK);
+#pragma unroll
+    for (int k = 0; k < LK; ++k) {
+      const float4 a0 = *(const float4*)&As[cur][k][ty * 4], a1 = *(const float4*)&As[cur][k][64 + ty * 4];
+      const float4 b0 = *(const float4*)&Ws[cur][k][tx * 4], b1 = *(const float4*)&Ws[cur][k][64 + tx * 4];
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    if (more) {
+      put(cur ^ 1);
+      __syncthreads();
+      cur ^= 1;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gm = m0 + (i >> 2) * 64 + ty * 4 + (i & 3);
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int gn = n0 + (j >> 2) * 64 + tx * 4 + (j & 3);
+      if (gn >= NW) continue;
+      if (EPI == EPI_SWIGLU_PAIRS) {
+        if (j & 1) continue;  // gate at the even weight row, up at the odd one after it
+        const float g = acc[i][j];
+        C[(size_t)gm * ldc + (gn >> 1)] = from_f32<TC>(g / (1.0f + expf(-g)) * acc[i][j + 1]);
+      } else {
+        TC* out = C + (size_t)gm * ldc + gn;
+        if (EPI == EPI_STORE) *out = from_f32<TC>(acc[i][j]);
+        else *out = from_f32<TC>(to_f32<TC>(*out) + acc[i][j]);
+      }
+    }
+  }
+}
+
 template <typename TA, typename TW, typename TC>
 static int launch(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K,
                   int epi, cudaStream_t s) {
@@ -201,6 +308,21 @@ static int launch(const void* A, int lda, const void* W, void* C, int ldc, int M
     else if (epi == EPI_SWIGLU) FEW(EPI_SWIGLU);
     else FEW(EPI_SWIGLU_PAIRS);
 #undef FEW
+    MB_CHECK_LAUNCH("mb_gemm_simt");
+  }
+  if (M >= 64 && epi != EPI_SWIGLU) {
+    const int NW = epi == EPI_SWIGLU_PAIRS ? 2 * N : N;
+    dim3 big((NW + LN - 1) / LN, (M + LM - 1) / LM);
+    if (big.y > 65535) MB_FAIL("mb_gemm_simt: %d rows are too many for one launch", M);
+    const int vec_a = K % 4 == 0 && lda % 4 == 0 && ((uintptr_t)A & a_align) == 0;
+    const int vec_w = K % 4 == 0 && ((uintptr_t)W & w_align) == 0;
+#define MANY(E)                                                                               \
+  gemm_many_rows_kernel<TA, TW, TC, E><<<big, 256, 0, s>>>((const TA*)A, lda, (const TW*)W,   \
+                                                           (TC*)C, ldc, M, NW, K, vec_a, vec_w)
+    if (epi == EPI_STORE) MANY(EPI_STORE);
+    else if (epi == EPI_ADD) MANY(EPI_ADD);
+    else MANY(EPI_SWIGLU_PAIRS);
+#undef MANY
     MB_CHECK_LAUNCH("mb_gemm_simt");
   }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
