@@ -120,6 +120,88 @@ __device__ __forceinline__ void store_row16(const float* v, void* C, int c_dtype
   }
 }
 
+// The epilogue of the forms with tokens on the lanes, for outputs made of whole 16-byte
+// pieces. A thread holds one accumulator row; written from there, a warp's store would touch
+// 32 rows with 32 bytes each. Instead the warp lays 32 rows x 128 bytes of finished output
+// into its own shared memory (`stage_w`, 4 KB; 16-byte pieces, piece p of row r at
+// p ^ (r & 7): no bank conflicts either way) and writes it out four whole rows of 128 bytes
+// at a time. `row0`: the warp's first row of the output; `width`: the tile's columns.
+__device__ __forceinline__ void staged_rows(uint32_t taddr, uint32_t stage_w, int lane, int row0,
+                                            int n0, int width, int M, int N, void* C, int c_dtype,
+                                            long long ldc, int mode, float* part,
+                                            long long partial_ld) {
+  const int acc_cols = mode == TC_SWIGLU ? 128 : (c_dtype == MB_BF16 && mode == TC_STORE ? 64 : 32);
+  const uint32_t mine = stage_w + lane * 128;
+#pragma unroll 1
+  for (int c0 = 0; c0 < width; c0 += acc_cols) {
+    if (n0 + c0 >= N) break;
+    const int ncols = min(acc_cols, min(width - c0, N - (n0 + c0)));
+#pragma unroll 1
+    for (int g = 0; g * 16 < ncols; ++g) {
+      float v[16];
+      tmem_ld16(taddr + c0 + 16 * g, v);
+      if (mode == TC_SWIGLU) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]),
+                                       silu_mul(v[4 * j + 2], v[4 * j + 3]));
+        st_shared_v4(mine + ((g ^ (lane & 7)) << 4), *(uint4*)&h[0]);
+      } else if (acc_cols == 64) {
+        __nv_bfloat162 h[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        st_shared_v4(mine + (((2 * g) ^ (lane & 7)) << 4), *(uint4*)&h[0]);
+        st_shared_v4(mine + (((2 * g + 1) ^ (lane & 7)) << 4), *(uint4*)&h[4]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          st_shared_v4(mine + (((4 * g + j) ^ (lane & 7)) << 4),
+                       make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                                  __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3])));
+      }
+    }
+    __syncwarp();
+    const int pc = lane & 7;
+    // bytes of output per accumulator column: 1 (SwiGLU), 2 (bfloat16), 4 (float32)
+    const int pieces = mode == TC_SWIGLU ? ncols >> 4 : (acc_cols == 64 ? ncols >> 3 : ncols >> 2);
+    if (acc_cols == 32) {
+      float* dst = mode == TC_PARTIAL ? part : (float*)C;
+      const long long ld = mode == TC_PARTIAL ? partial_ld : ldc;
+      float4 old[8];
+      if (mode == TC_ADD) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = 4 * i + (lane >> 3);
+          if (pc < pieces && row0 + r < M)
+            old[i] = *(const float4*)(dst + (size_t)(row0 + r) * ld + n0 + c0 + 4 * pc);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = 4 * i + (lane >> 3);
+        if (pc < pieces && row0 + r < M) {
+          const uint4 u = ld_shared_v4(stage_w + r * 128 + ((pc ^ (r & 7)) << 4));
+          float4 o = make_float4(__uint_as_float(u.x), __uint_as_float(u.y),
+                                 __uint_as_float(u.z), __uint_as_float(u.w));
+          if (mode == TC_ADD) { o.x += old[i].x; o.y += old[i].y; o.z += old[i].z; o.w += old[i].w; }
+          *(float4*)(dst + (size_t)(row0 + r) * ld + n0 + c0 + 4 * pc) = o;
+        }
+      }
+    } else {
+      const int col = (mode == TC_SWIGLU ? (n0 + c0) >> 1 : n0 + c0) + 8 * pc;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = 4 * i + (lane >> 3);
+        if (pc < pieces && row0 + r < M)
+          *(uint4*)((__nv_bfloat16*)C + (size_t)(row0 + r) * ldc + col) =
+              ld_shared_v4(stage_w + r * 128 + ((pc ^ (r & 7)) << 4));
+      }
+    }
+    __syncwarp();  // the rows are read out before the next columns are laid over them
+  }
+}
+
 // rowsA x rowsB outputs: element (a, b) is the dot product of row a of the lanes' operand and
 // row b of the columns' operand. SWAP false: C[a * ldc + b]; true: C[b * ldc + a].
 // A CTA owns `tile_rows` (<= 128) rows of the lanes' operand; its stages hold a_stage bytes of
@@ -150,6 +232,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nkb_total = (K + TC_BK - 1) / TC_BK;
   const int tiles_ab = tiles_a * tiles_b;
+  // tokens on the lanes: the epilogue warps' staging rows lie behind the barriers (the host
+  // adds their 16 KB); whole 16-byte pieces of output need a width, a row stride and a base
+  // that are multiples of 16 bytes
+  const uint32_t stage_w = bars + 1024 + (warp & 3) * 4096;
+  const int out_cols = mode == TC_SWIGLU ? rowsB >> 1 : rowsB;
+  const int per16 = (mode == TC_SWIGLU || (mode == TC_STORE && c_dtype == MB_BF16)) ? 8 : 4;
+  const bool staged = !SWAP && out_cols % per16 == 0 &&
+                      (mode == TC_PARTIAL ? (partial_ld % 4 == 0 && partial_stride % 4 == 0 &&
+                                             ((uintptr_t)partial & 15) == 0)
+                                          : (ldc % per16 == 0 && ((uintptr_t)C & 15) == 0));
   const uint32_t stage_bytes = (uint32_t)tile_rows * (TC_BK * 2) + Cfg::B_BYTES;
 
   if (threadIdx.x == 0) {
@@ -256,6 +348,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const bool mine = lane_row < tile_rows && a < rowsA;
       const uint32_t taddr = tmem + b * Cfg::COLS + ((uint32_t)(q * 32) << 16);
       float* part = partial ? partial + z * partial_stride : nullptr;
+      if (staged) {
+        staged_rows(taddr, stage_w, lane, a - lane, n0, BN, rowsA, rowsB, C, c_dtype, ldc, mode,
+                    part, partial_ld);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty0 + 8 * b);
+        continue;
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         if (n0 + c0 >= rowsB) break;  // uniform over the warp
@@ -437,82 +537,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t taddr = tmem + b * TC2_COLS + ((uint32_t)(q * 32) << 16);
       float* part = partial ? partial + z * partial_stride : nullptr;
       if (staged) {
-        // A thread holds one accumulator row; written from there, a warp's store would touch
-        // 32 rows with 32 bytes each. Instead the warp lays 32 rows x 128 bytes of finished
-        // output into its own shared memory (16-byte pieces, piece p of row r at
-        // p ^ (r & 7): no bank conflicts either way) and writes it out four whole rows of
-        // 128 bytes at a time.
-        const int row0 = a - lane;  // the warp's first row
-        const int acc_cols = mode == TC_SWIGLU ? 128 : (c_dtype == MB_BF16 && mode == TC_STORE ? 64 : 32);
-        const uint32_t mine = stage_w + lane * 128;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += acc_cols) {
-          if (n0 + c0 >= N) break;
-          const int ncols = min(acc_cols, min(BN - c0, N - (n0 + c0)));
-#pragma unroll 1
-          for (int g = 0; g * 16 < ncols; ++g) {
-            float v[16];
-            tmem_ld16(taddr + c0 + 16 * g, v);
-            if (mode == TC_SWIGLU) {
-              __nv_bfloat162 h[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]),
-                                             silu_mul(v[4 * j + 2], v[4 * j + 3]));
-              st_shared_v4(mine + ((g ^ (lane & 7)) << 4), *(uint4*)&h[0]);
-            } else if (acc_cols == 64) {
-              __nv_bfloat162 h[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-              st_shared_v4(mine + (((2 * g) ^ (lane & 7)) << 4), *(uint4*)&h[0]);
-              st_shared_v4(mine + (((2 * g + 1) ^ (lane & 7)) << 4), *(uint4*)&h[4]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                st_shared_v4(mine + (((4 * g + j) ^ (lane & 7)) << 4),
-                             make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
-                                        __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3])));
-            }
-          }
-          __syncwarp();
-          const int pc = lane & 7;
-          // bytes of output per accumulator column: 1 (SwiGLU), 2 (bfloat16), 4 (float32)
-          const int pieces = mode == TC_SWIGLU ? ncols >> 4 : (acc_cols == 64 ? ncols >> 3 : ncols >> 2);
-          if (acc_cols == 32) {
-            float* dst = mode == TC_PARTIAL ? part : (float*)C;
-            const long long ld = mode == TC_PARTIAL ? partial_ld : ldc;
-            float4 old[8];
-            if (mode == TC_ADD) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const int r = 4 * i + (lane >> 3);
-                if (pc < pieces && row0 + r < M)
-                  old[i] = *(const float4*)(dst + (size_t)(row0 + r) * ld + n0 + c0 + 4 * pc);
-              }
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int r = 4 * i + (lane >> 3);
-              if (pc < pieces && row0 + r < M) {
-                const uint4 u = ld_shared_v4(stage_w + r * 128 + ((pc ^ (r & 7)) << 4));
-                float4 o = make_float4(__uint_as_float(u.x), __uint_as_float(u.y),
-                                       __uint_as_float(u.z), __uint_as_float(u.w));
-                if (mode == TC_ADD) { o.x += old[i].x; o.y += old[i].y; o.z += old[i].z; o.w += old[i].w; }
-                *(float4*)(dst + (size_t)(row0 + r) * ld + n0 + c0 + 4 * pc) = o;
-              }
-            }
-          } else {
-            const int col = (mode == TC_SWIGLU ? (n0 + c0) >> 1 : n0 + c0) + 8 * pc;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int r = 4 * i + (lane >> 3);
-              if (pc < pieces && row0 + r < M)
-                *(uint4*)((__nv_bfloat16*)C + (size_t)(row0 + r) * ldc + col) =
-                    ld_shared_v4(stage_w + r * 128 + ((pc ^ (r & 7)) << 4));
-            }
-          }
-          __syncwarp();  // the rows are read out before the next columns are laid over them
-        }
+        staged_rows(taddr, stage_w, lane, a - lane, n0, BN, M, N, C, c_dtype, ldc, mode, part,
+                    partial_ld);
       } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -749,6 +775,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     p.tile_rows = TC_BM;
     p.max_ctas = sms;
     plan_stages(p, bn, 200 * 1024);
+    p.smem += 4 * 4096;  // the epilogue warps' staging rows
     const int tiles = ((rowsA + TC_BM - 1) / TC_BM) * ((rowsB + bn - 1) / bn);
     if (workspace && epilogue != TC_SWIGLU && tiles < sms && nkb >= 8) {
       int want = (2 * sms + tiles - 1) / tiles;
