@@ -18,10 +18,21 @@ enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_SWIGLU_PAIRS = 3 };
 #define BN 64
 #define BK 16
 
-template <typename TA, typename TW, typename TC, int EPI>
+// The output's type is looked at when a result is stored, not compiled in: eight variants of
+// every kernel less to build.
+__device__ __forceinline__ void put_out(void* C, int c_bf16, size_t at, float v, bool add) {
+  if (c_bf16) {
+    ((__nv_bfloat16*)C)[at] = __float2bfloat16_rn(v);  // a residual add is float32 only
+  } else {
+    float* out = (float*)C + at;
+    *out = add ? *out + v : v;
+  }
+}
+
+template <typename TA, typename TW, int EPI>
 __global__ void __launch_bounds__(256)
-gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, TC* __restrict__ C,
-                 int ldc, int M, int N, int K) {
+gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, void* __restrict__ C,
+                 int c_bf16, int ldc, int M, int N, int K) {
   constexpr int NW = (EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_PAIRS) ? 2 : 1;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[NW][BK][BN + 4];
@@ -79,15 +90,12 @@ gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, TC
     for (int j = 0; j < 4; ++j) {
       const int gn = n0 + tc + j;
       if (gn >= N) continue;
-      TC* out = C + (size_t)gm * ldc + gn;
-      if (EPI == EPI_STORE) {
-        *out = from_f32<TC>(acc[0][i][j]);
-      } else if (EPI == EPI_ADD) {
-        *out = from_f32<TC>(to_f32<TC>(*out) + acc[0][i][j]);
+      const size_t at = (size_t)gm * ldc + gn;
+      if (EPI == EPI_STORE || EPI == EPI_ADD) {
+        put_out(C, c_bf16, at, acc[0][i][j], EPI == EPI_ADD);
       } else {
         const float g = acc[0][i][j];
-        const float b = g / (1.0f + expf(-g));
-        *out = from_f32<TC>(b * acc[NW - 1][i][j]);
+        put_out(C, c_bf16, at, g / (1.0f + expf(-g)) * acc[NW - 1][i][j], false);
       }
     }
   }
@@ -120,10 +128,10 @@ template <> __device__ __forceinline__ float4 load4_once<__nv_bfloat16>(const __
 #define FEW_ROWS 8   // rows of A in one pass
 #define FEW_MAX 16   // the most rows that take this kernel
 
-template <typename TA, typename TW, typename TC, int EPI>
+template <typename TA, typename TW, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_few_rows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W,
-                     TC* __restrict__ C, int ldc, int M, int N, int K) {
+                     void* __restrict__ C, int c_bf16, int ldc, int M, int N, int K) {
   constexpr bool GLU = EPI == EPI_SWIGLU || EPI == EPI_SWIGLU_PAIRS;
   constexpr int FEATS = GLU ? 2 : 4;  // output features of a warp
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -169,15 +177,13 @@ gemm_few_rows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W
 #pragma unroll
       for (int f = 0; f < FEATS; ++f) {
         if (n0 + f >= N) continue;
-        TC* out = C + (size_t)(m0 + m) * ldc + n0 + f;
-        if (EPI == EPI_STORE) {
-          *out = from_f32<TC>(acc[f][m]);
-        } else if (EPI == EPI_ADD) {
-          *out = from_f32<TC>(to_f32<TC>(*out) + acc[f][m]);
+        const size_t at = (size_t)(m0 + m) * ldc + n0 + f;
+        if (EPI == EPI_STORE || EPI == EPI_ADD) {
+          put_out(C, c_bf16, at, acc[f][m], EPI == EPI_ADD);
         } else {
           const float g = EPI == EPI_SWIGLU ? acc[f][m] : acc[2 * f][m];
           const float u = EPI == EPI_SWIGLU ? acc[2 + f][m] : acc[2 * f + 1][m];
-          *out = from_f32<TC>(g / (1.0f + expf(-g)) * u);
+          put_out(C, c_bf16, at, g / (1.0f + expf(-g)) * u, false);
         }
       }
     }
@@ -208,10 +214,11 @@ __device__ __forceinline__ float4 row_piece(const T* __restrict__ base, bool row
   return v;
 }
 
-template <typename TA, typename TW, typename TC, int EPI>
+template <typename TA, typename TW, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_many_rows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W,
-                      TC* __restrict__ C, int ldc, int M, int NW, int K, int vec_a, int vec_w) {
+                      void* __restrict__ C, int c_bf16, int ldc, int M, int NW, int K, int vec_a,
+                      int vec_w) {
   __shared__ __align__(16) float As[2][LK][LM + 4];
   __shared__ __align__(16) float Ws[2][LK][LN + 4];
   const int tid = threadIdx.x;
@@ -281,19 +288,17 @@ gemm_many_rows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ 
       if (EPI == EPI_SWIGLU_PAIRS) {
         if (j & 1) continue;  // gate at the even weight row, up at the odd one after it
         const float g = acc[i][j];
-        C[(size_t)gm * ldc + (gn >> 1)] = from_f32<TC>(g / (1.0f + expf(-g)) * acc[i][j + 1]);
+        put_out(C, c_bf16, (size_t)gm * ldc + (gn >> 1), g / (1.0f + expf(-g)) * acc[i][j + 1], false);
       } else {
-        TC* out = C + (size_t)gm * ldc + gn;
-        if (EPI == EPI_STORE) *out = from_f32<TC>(acc[i][j]);
-        else *out = from_f32<TC>(to_f32<TC>(*out) + acc[i][j]);
+        put_out(C, c_bf16, (size_t)gm * ldc + gn, acc[i][j], EPI == EPI_ADD);
       }
     }
   }
 }
 
-template <typename TA, typename TW, typename TC>
-static int launch(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, int K,
-                  int epi, cudaStream_t s) {
+template <typename TA, typename TW>
+static int launch(const void* A, int lda, const void* W, void* C, int c_bf16, int ldc, int M, int N,
+                  int K, int epi, cudaStream_t s) {
   // few rows, and every row piece of 4 values a whole aligned load
   const int a_align = sizeof(TA) == 4 ? 15 : 7, w_align = sizeof(TW) == 4 ? 15 : 7;
   if (M <= FEW_MAX && K % 4 == 0 && lda % 4 == 0 && ((uintptr_t)A & a_align) == 0 &&
@@ -301,8 +306,8 @@ static int launch(const void* A, int lda, const void* W, void* C, int ldc, int M
     const int feats = (epi == EPI_SWIGLU || epi == EPI_SWIGLU_PAIRS) ? 2 : 4;
     const int blocks = (N + 8 * feats - 1) / (8 * feats);
 #define FEW(E)                                                                                \
-  gemm_few_rows_kernel<TA, TW, TC, E><<<blocks, 256, 0, s>>>((const TA*)A, lda, (const TW*)W, \
-                                                             (TC*)C, ldc, M, N, K)
+  gemm_few_rows_kernel<TA, TW, E><<<blocks, 256, 0, s>>>((const TA*)A, lda, (const TW*)W, C,  \
+                                                         c_bf16, ldc, M, N, K)
     if (epi == EPI_STORE) FEW(EPI_STORE);
     else if (epi == EPI_ADD) FEW(EPI_ADD);
     else if (epi == EPI_SWIGLU) FEW(EPI_SWIGLU);
@@ -317,8 +322,8 @@ static int launch(const void* A, int lda, const void* W, void* C, int ldc, int M
     const int vec_a = K % 4 == 0 && lda % 4 == 0 && ((uintptr_t)A & a_align) == 0;
     const int vec_w = K % 4 == 0 && ((uintptr_t)W & w_align) == 0;
 #define MANY(E)                                                                               \
-  gemm_many_rows_kernel<TA, TW, TC, E><<<big, 256, 0, s>>>((const TA*)A, lda, (const TW*)W,   \
-                                                           (TC*)C, ldc, M, NW, K, vec_a, vec_w)
+  gemm_many_rows_kernel<TA, TW, E><<<big, 256, 0, s>>>((const TA*)A, lda, (const TW*)W, C,    \
+                                                       c_bf16, ldc, M, NW, K, vec_a, vec_w)
     if (epi == EPI_STORE) MANY(EPI_STORE);
     else if (epi == EPI_ADD) MANY(EPI_ADD);
     else MANY(EPI_SWIGLU_PAIRS);
@@ -328,8 +333,8 @@ static int launch(const void* A, int lda, const void* W, void* C, int ldc, int M
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) MB_FAIL("mb_gemm_simt: %d rows are too many for one launch", M);
 #define GO(E)                                                                                  \
-  gemm_simt_kernel<TA, TW, TC, E><<<grid, 256, 0, s>>>((const TA*)A, lda, (const TW*)W, (TC*)C, \
-                                                       ldc, M, N, K)
+  gemm_simt_kernel<TA, TW, E><<<grid, 256, 0, s>>>((const TA*)A, lda, (const TW*)W, C, c_bf16,  \
+                                                   ldc, M, N, K)
   if (epi == EPI_STORE) GO(EPI_STORE);
   else if (epi == EPI_ADD) GO(EPI_ADD);
   else if (epi == EPI_SWIGLU) GO(EPI_SWIGLU);
@@ -349,15 +354,10 @@ MB_EXPORT int mb_gemm_simt(const void* A, int a_dtype, int lda, const void* W, i
   if (epilogue == EPI_ADD && c_dtype != MB_F32) MB_FAIL("mb_gemm_simt: the residual is float32");
   cudaStream_t s = (cudaStream_t)stream;
   typedef __nv_bfloat16 bf;
-  const int key = (a_dtype << 2) | (w_dtype << 1) | c_dtype;
-  switch (key) {
-    case 0: return launch<float, float, float>(A, lda, W, C, ldc, M, N, K, epilogue, s);
-    case 1: return launch<float, float, bf>(A, lda, W, C, ldc, M, N, K, epilogue, s);
-    case 2: return launch<float, bf, float>(A, lda, W, C, ldc, M, N, K, epilogue, s);
-    case 3: return launch<float, bf, bf>(A, lda, W, C, ldc, M, N, K, epilogue, s);
-    case 4: return launch<bf, float, float>(A, lda, W, C, ldc, M, N, K, epilogue, s);
-    case 5: return launch<bf, float, bf>(A, lda, W, C, ldc, M, N, K, epilogue, s);
-    case 6: return launch<bf, bf, float>(A, lda, W, C, ldc, M, N, K, epilogue, s);
-    default: return launch<bf, bf, bf>(A, lda, W, C, ldc, M, N, K, epilogue, s);
-  }
+  const int c_bf16 = c_dtype == MB_BF16;
+  if (a_dtype == MB_F32 && w_dtype == MB_F32)
+    return launch<float, float>(A, lda, W, C, c_bf16, ldc, M, N, K, epilogue, s);
+  if (a_dtype == MB_F32) return launch<float, bf>(A, lda, W, C, c_bf16, ldc, M, N, K, epilogue, s);
+  if (w_dtype == MB_F32) return launch<bf, float>(A, lda, W, C, c_bf16, ldc, M, N, K, epilogue, s);
+  return launch<bf, bf>(A, lda, W, C, c_bf16, ldc, M, N, K, epilogue, s);
 }
