@@ -787,10 +787,9 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     p.kb_per_split = (nkb + p.splits - 1) / p.splits;
     p.splits = (nkb + p.kb_per_split - 1) / p.kb_per_split;
   }
-  const int pairs = (!swap && N >= 256 && M > 128 &&
-                     (M % 256 == 0 || M % 256 > 128 || M >= 1024))
-                        ? pair_capacity(sms)
-                        : 0;
+  // more than 128 tokens: tiles of 256 tokens on CTA pairs, even where the last tile is
+  // mostly empty (520 tokens: 10.2 ms a pass of the 8B shape against 11.4 on single CTAs)
+  const int pairs = (!swap && N >= 256 && M > 128) ? pair_capacity(sms) : 0;
   if (pairs > 0) {
     const int tiles_m = (M + 255) / 256;
     const int bn = pair_tile_width(N, tiles_m, pairs);
