@@ -76,6 +76,12 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// the largest of three in one instruction
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -316,14 +322,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
           if (!(key >= lo && key <= pos)) s[c] = -INFINITY;
         }
       }
-      // four chains, so that the maximum (and the sum below) does not wait on itself
+      // The maximum of the raw scores (the scale is positive, so it is the maximum of the
+      // scaled ones too), two scores an instruction in four chains; the scale itself goes into
+      // the multiply-add in front of the exponential below.
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < MB_PAGE; ++c) {
-        s[c] *= scale_log2;
-        mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      for (int c = 0; c < MB_PAGE; c += 2) mx4[(c >> 1) & 3] = max3(mx4[(c >> 1) & 3], s[c], s[c + 1]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       // O is rescaled only when this row's maximum has grown by more than 2^8 (or appears for
       // the first time); until then the old reference stays and P may reach 2^8
       const bool grow = mx > m_ref + 8.0f || (m_ref == -INFINITY && mx > -INFINITY);
@@ -355,7 +360,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2(s[c16 * 32 + 2 * i] - ref), p1 = ex2(s[c16 * 32 + 2 * i + 1] - ref);
+          const float p0 = ex2(fmaf(s[c16 * 32 + 2 * i], scale_log2, -ref));
+          const float p1 = ex2(fmaf(s[c16 * 32 + 2 * i + 1], scale_log2, -ref));
           l4[i & 3] += p0 + p1;
           __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
           w[i] = *reinterpret_cast<uint32_t*>(&v);
@@ -427,6 +433,8 @@ MB_EXPORT int mb_attention_prefill_tc(const void* q, int q_stride, int q_cols, v
   if (((uintptr_t)out & 15) || (out_stride & 7))
     MB_FAIL("mb_attention_prefill_tc: out is not 16-byte aligned (stride %d)", out_stride);
   if (B > 65535 || nh > 65535) MB_FAIL("mb_attention_prefill_tc: %d sequences, %d heads", B, nh);
+  if (!(scale > 0.f))  // the row maximum is taken over the scores before they are scaled
+    MB_FAIL("mb_attention_prefill_tc: a scale of %g (it must be positive)", (double)scale);
   CUtensorMap tmQ, tmK, tmV;
   if (!mb_make_map_bf16(&tmQ, q, T, q_cols, q_stride, AT_ROWS, "mb_attention_prefill_tc q")) return -1;
   if (!mb_make_map_bf16(&tmK, kpool, pool_rows, hd, hd, MB_PAGE, "mb_attention_prefill_tc k")) return -1;
