@@ -76,6 +76,26 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// two float32 values in one 64-bit register, and arithmetic on both at once
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long r, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b,
+                                                   unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 // the largest of three in one instruction
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float y;
@@ -354,21 +374,28 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
       const float ref = m_ref == -INFINITY ? 0.f : m_ref;
       // P over the S just read, as the first operand of the second product: this thread's row,
       // two bfloat16 values a column, keys in order
-      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      // (two scores a multiply-add and two a sum: the exponentials need the issue slots)
+      const unsigned long long scale2 = pack2(scale_log2, scale_log2), ref2 = pack2(-ref, -ref);
+      unsigned long long l4[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
       for (int c16 = 0; c16 < 2; ++c16) {
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2(fmaf(s[c16 * 32 + 2 * i], scale_log2, -ref));
-          const float p1 = ex2(fmaf(s[c16 * 32 + 2 * i + 1], scale_log2, -ref));
-          l4[i & 3] += p0 + p1;
+          float x0, x1;
+          unpack2(fma2(pack2(s[c16 * 32 + 2 * i], s[c16 * 32 + 2 * i + 1]), scale2, ref2), x0, x1);
+          const float p0 = ex2(x0), p1 = ex2(x1);
+          l4[i & 3] = add2(l4[i & 3], pack2(p0, p1));
           __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
           w[i] = *reinterpret_cast<uint32_t*>(&v);
         }
         tmem_st16_u32(tSj + 16 * c16, w);
       }
-      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      {
+        float a0, a1;
+        unpack2(add2(add2(l4[0], l4[1]), add2(l4[2], l4[3])), a0, a1);
+        l += a0 + a1;
+      }
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
