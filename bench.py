@@ -442,6 +442,15 @@ def main():
             (bms, held, _), rec = clocked(timed_decode, torch, eng, sampler, greedy, lens, steps,
                                           a.warmup, 10 + b)
             pts.decode(f"decode_b{b}", cfg, bms, steps, b, held, rec)
+        # the same batches (and the headline's) at shorter contexts: the weights' share of a step
+        # grows as the cache's shrinks
+        for ctx in (512, 2304):
+            for b in sorted(set([BATCH] + [int(v) for v in a.batches.split(',') if v])):
+                steps = min(a.steps, 64)
+                lens = [ctx - steps - a.warmup - SETTLE] * b
+                (bms, held, _), rec = clocked(timed_decode, torch, eng, sampler, greedy, lens,
+                                              steps, a.warmup, 100 + b + ctx)
+                pts.decode(f"decode_b{b}_ctx{ctx}", cfg, bms, steps, b, held, rec)
         e1_ms, _, _ = timed_e2e(torch, eng, 1, min(a.steps, 128), a.warmup, 3)
         pts.values["e2e_b1"] = round(min(a.steps, 128) / (e1_ms / 1e3), 1)
         del eng, sampler
