@@ -219,6 +219,7 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   return u;
 }
 
+#define QK_PASSES 3  // groups of heads that a warp of the wide form takes, at most
 template <int HD, bool PARTIAL>
 __global__ void __launch_bounds__(QK_WARPS * 32)
 qk_wide_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partial, int parts,
@@ -241,7 +242,25 @@ qk_wide_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partia
   const int group0 = (blockIdx.y * (blockDim.x >> 5) + warp) * passes;
   float cs[8], sn[8];
   bool have_angles = false;
-  for (int i = 0; i < passes; ++i) {
+  // every pass's values are asked for before the first pass is worked on: a pass's stores
+  // may lie over the next one's source (q is rotated in place), so the compiler would not
+  // move the loads up by itself, and three round trips to memory in a row would set the time
+  uint4 raw[QK_PASSES][2];
+  if (!PARTIAL) {
+#pragma unroll
+    for (int i = 0; i < QK_PASSES; ++i) {
+      const int head = (group0 + i) * HPP + hl;
+      raw[i][0] = raw[i][1] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < passes && head < total && (head < nh || write_kv)) {
+        const __nv_bfloat16* src = qkv + (size_t)t * total * HD + (size_t)head * HD + 8 * sl;
+        raw[i][0] = *reinterpret_cast<const uint4*>(src);
+        raw[i][1] = *reinterpret_cast<const uint4*>(src + HALF);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < QK_PASSES; ++i) {
+    if (i >= passes) break;
     const int head0 = (group0 + i) * HPP;
     if (head0 >= total) break;  // the whole warp
     const int head = head0 + hl;
@@ -265,9 +284,8 @@ qk_wide_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partia
           b[4] += b1.x; b[5] += b1.y; b[6] += b1.z; b[7] += b1.w;
         }
       } else {
-        const __nv_bfloat16* src = qkv + (size_t)t * total * HD + col;
-        unpack8(*reinterpret_cast<const uint4*>(src), a);
-        unpack8(*reinterpret_cast<const uint4*>(src + HALF), b);
+        unpack8(raw[i][0], a);
+        unpack8(raw[i][1], b);
       }
     }
     if (head0 < nh + nkv) {  // some head of this pass is a q or k head (uniform over the warp)
@@ -368,7 +386,7 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
     }
     // groups of 512 / hd heads: blocks of four warps that take three groups each
     const int groups = ((nh + 2 * nkv) * hd + 511) / 512;
-    const int warps = QK_WARPS, passes = 3;
+    const int warps = QK_WARPS, passes = QK_PASSES;
     dim3 fgrid(T, (groups + warps * passes - 1) / (warps * passes));
 #define QKF(HD_, P_)                                                                           \
   mb_launch(qk_wide_kernel<HD_, P_>, fgrid, dim3(warps * 32), 0, s, (bf*)qkv, partial, parts,  \
